@@ -1,0 +1,111 @@
+"""B200 (sm_100a) drop-in for the attention hot path of HPC-SJTU/af3_kernels.
+
+The public names and signatures follow the reference's ``src/af3_kernels/__init__.py``.  Only
+the biased, key-masked dot-product attention path is implemented (hand-written CUDA behind
+``libaf3k.so``); the reference's other operators are importable but raise
+``NotImplementedError``.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _capi
+from .dpa import dot_product_attention, read_status
+from .tools import pad_to_size, print_comm_time, profile, record_comm_time
+from .distributed import RowShardedAttention, row_partition
+
+__all__ = [
+    "dot_product_attention_cpp",
+    "dot_product_attention",
+    "RowShardedAttention",
+    "row_partition",
+    "gated_linear_unit_cpp",
+    "_attention_cpp",
+    "self_attention_cpp",
+    "pad_and_align_tensor",
+    "vnni_repack_tensor",
+    "reset_debug_timers",
+    "print_debug_timers",
+    "print_debug_thread_imbalance",
+]
+
+
+@profile("dot_product_attention")
+def dot_product_attention_cpp(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    mask: torch.Tensor,
+    bias: torch.Tensor,
+    use_flash_attention: bool = False,
+    BLK_SZ: int = 128,
+    FLASH_SZ: int = 1024,
+    *,
+    q_scale: Optional[torch.Tensor] = None,
+    k_scale: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Same positional signature as the reference (src/af3_kernels/__init__.py:31-40).
+
+    ``use_flash_attention``, ``BLK_SZ`` and ``FLASH_SZ`` are accepted and checked but do not
+    select code: the CUDA kernel always runs an online softmax over 128-key tiles.  Unlike the
+    reference the call never writes to ``q`` and a 1-D mask broadcasts over the batch.
+    ``q_scale`` / ``k_scale`` (keyword-only) enable float8_e4m3fn q and k.
+    """
+    if int(BLK_SZ) <= 0 or int(FLASH_SZ) <= 0:
+        raise ValueError("BLK_SZ and FLASH_SZ must be positive")
+    return dot_product_attention(q, k, v, mask, bias, q_scale=q_scale, k_scale=k_scale)
+
+
+def _not_built(name: str):
+    raise NotImplementedError(
+        f"{name} is outside the attention hot path this package implements on B200"
+    )
+
+
+def gated_linear_unit_cpp(x, weight, vnni_repacked=False, M_BLK=128, N_BLK=128):
+    _not_built("gated_linear_unit_cpp")
+
+
+def _attention_cpp(pair, mask, bias, q_proj, k_proj, v_proj, gating_query, out_proj, head,
+                   use_flash_attention=False, BLK_SZ=128, FLASH_SZ=1024):
+    _not_built("_attention_cpp")
+
+
+def self_attention_cpp(pair, mask, bias, q_proj, q_bias, k_proj, v_proj, gating_query, head,
+                       use_flash_attention=False, BLK_SZ=128, FLASH_SZ=1024):
+    _not_built("self_attention_cpp")
+
+
+def pad_and_align_tensor(x: torch.Tensor, shape, need_init: bool = True, init: float = 0.0,
+                         alignment: int = 64) -> torch.Tensor:
+    """Device-side stand-in for the reference helper (src/csrc/tools.cpp:42-124): returns ``x``
+    itself when it already has ``shape`` and is contiguous, else a new tensor of ``shape`` holding
+    ``x`` in its leading corner and ``init`` elsewhere.  The kernel needs no padding (TMA
+    zero-fills out-of-range tiles); this exists for callers that used the helper directly."""
+    shape = tuple(int(s) for s in shape)
+    if tuple(x.shape) == shape and x.is_contiguous():
+        return x
+    if len(shape) != x.dim() or any(a > b for a, b in zip(x.shape, shape)):
+        raise ValueError(f"cannot pad {tuple(x.shape)} to {shape}")
+    out = torch.full(shape, init, dtype=x.dtype, device=x.device) if need_init else \
+        torch.empty(shape, dtype=x.dtype, device=x.device)
+    out[tuple(slice(0, s) for s in x.shape)] = x
+    return out
+
+
+def vnni_repack_tensor(x: torch.Tensor, type: int = 2, BLK_SZ: int = 0) -> torch.Tensor:
+    _not_built("vnni_repack_tensor (a CPU VNNI layout; TMA swizzled tiles replace it on B200)")
+
+
+def reset_debug_timers():
+    """The reference resets per-thread rdtsc timers (src/csrc/init.cpp:102-143); kept as a no-op."""
+
+
+def print_debug_timers(tid=0, detailed=True):
+    """No CPU-thread timers exist here; use CUDA events or torch.profiler (DO_PROFILE=1)."""
+
+
+def print_debug_thread_imbalance():
+    """See print_debug_timers."""

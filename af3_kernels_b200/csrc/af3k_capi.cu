@@ -1,0 +1,417 @@
+// C ABI of libaf3k.so (declared in include/af3k.h): argument validation, launch planning,
+// TMA descriptor encoding and kernel launches.  No torch types cross this boundary.
+#include "../../include/af3k.h"
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include "attn_sm100.cuh"
+
+namespace {
+
+using namespace af3k;
+
+std::atomic<long long> g_wait_limit{-1};
+thread_local int t_last_launches = 0;
+std::atomic<float*> g_debug_dump{nullptr};
+thread_local char t_detail[256] = "";
+
+// Records which CUDA call failed (text returned by af3k_last_error_detail) and clears the
+// runtime's sticky-until-read error so that it does not surface in the caller's next CUDA call.
+int cuda_fail(const char* what, cudaError_t e) {
+  std::snprintf(t_detail, sizeof(t_detail), "%s: %s", what, cudaGetErrorString(e));
+  (void)cudaGetLastError();
+  return AF3K_ERR_CUDA;
+}
+int driver_fail(const char* what, int r) {
+  std::snprintf(t_detail, sizeof(t_detail), "%s: CUresult %d", what, r);
+  return AF3K_ERR_CUDA;
+}
+
+long long wait_limit_cycles() {
+  long long v = g_wait_limit.load();
+  if (v > 0) return v;
+  const char* e = std::getenv("AF3K_WAIT_LIMIT_CYCLES");
+  v = e ? std::atoll(e) : 0;
+  if (v <= 0) v = 2000000000LL;
+  g_wait_limit.store(v);
+  return v;
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  });
+  return fn;
+}
+
+constexpr int kStaticSmemReserve = 256;
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int cc_major = 0;
+  int max_smem_optin = 0;
+  bool attr_set = false;
+};
+
+int device_info(DeviceInfo** out) {
+  static DeviceInfo infos[64];
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) return cuda_fail("cudaGetDevice", e);
+  std::lock_guard<std::mutex> lock(mu);
+  DeviceInfo& d = infos[dev];
+  if (d.sm_count == 0) {
+    cudaDeviceProp prop;
+    if ((e = cudaGetDeviceProperties(&prop, dev)) != cudaSuccess)
+      return cuda_fail("cudaGetDeviceProperties", e);
+    d.sm_count = prop.multiProcessorCount;
+    d.cc_major = prop.major;
+    d.max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+  }
+  if (d.cc_major != 10) return AF3K_ERR_UNSUPPORTED_DEVICE;
+  if (!d.attr_set) {
+    // the opt-in limit covers static + dynamic shared memory; the kernel has a few static bytes
+    const int dyn = d.max_smem_optin - kStaticSmemReserve;
+    if ((e = cudaFuncSetAttribute(attention_kernel<false>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dyn)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(attention_kernel<true>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dyn)) != cudaSuccess)
+      return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize)", e);
+    d.attr_set = true;
+  }
+  *out = &d;
+  return AF3K_OK;
+}
+
+int row_bytes_for(int64_t bytes) { return bytes <= 32 ? 32 : (bytes <= 64 ? 64 : 128); }
+CUtensorMapSwizzle swizzle_for(int row_bytes) {
+  return row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Does the bias need the bf16 staging copy?
+bool bias_needs_staging(const af3k_attention_desc& d, const void* bias) {
+  if (d.bias_dtype != AF3K_BF16) return true;
+  if ((d.bias_stride[0] * 2) % 16 != 0 || (d.bias_stride[1] * 2) % 16 != 0) return true;
+  if (bias != nullptr && !aligned16(bias)) return true;
+  return false;
+}
+int64_t staged_bias_pitch(int64_t Sk) { return (Sk + 7) / 8 * 8; }
+
+int validate(const af3k_attention_desc& d) {
+  if (d.qk_dtype != AF3K_BF16 && d.qk_dtype != AF3K_FP8_E4M3) return AF3K_ERR_BAD_DTYPE;
+  if (d.bias_dtype != AF3K_BF16 && d.bias_dtype != AF3K_F32) return AF3K_ERR_BAD_DTYPE;
+  if (d.B1 < 0 || d.B2 < 0 || d.Sq < 0 || d.Sk <= 0 || d.D <= 0) return AF3K_ERR_BAD_SHAPE;
+  if (d.D % 8 != 0 || d.D > 64) return AF3K_ERR_BAD_SHAPE;
+  if (d.qk_dtype == AF3K_FP8_E4M3 && d.D % 16 != 0) return AF3K_ERR_BAD_SHAPE;
+  if (d.B1 > 0x7fffffff || d.B2 > 0x7fffffff || d.Sq > 0x7fffff00 || d.Sk > 0x7fffff00)
+    return AF3K_ERR_BAD_SHAPE;
+  if (d.rows_per_item < 0 || d.rows_per_item > kMaxStreams) return AF3K_ERR_BAD_SHAPE;
+  const int64_t es = d.qk_dtype == AF3K_FP8_E4M3 ? 1 : 2;
+  for (int i = 0; i < 3; ++i) {
+    if (d.q_stride[i] < 0 || d.k_stride[i] < 0 || d.v_stride[i] < 0 || d.out_stride[i] < 0)
+      return AF3K_ERR_BAD_STRIDE;
+    if ((d.q_stride[i] * es) % 16 || (d.k_stride[i] * es) % 16 || (d.v_stride[i] * 2) % 16 ||
+        (d.out_stride[i] * 2) % 16)
+      return AF3K_ERR_BAD_STRIDE;
+  }
+  if (d.q_stride[2] < d.D || d.k_stride[2] < d.D || d.v_stride[2] < d.D || d.out_stride[2] < d.D)
+    return AF3K_ERR_BAD_STRIDE;
+  if (d.bias_stride[0] < 0 || d.bias_stride[1] < d.Sk || d.mask_row_stride < 0)
+    return AF3K_ERR_BAD_STRIDE;
+  return AF3K_OK;
+}
+
+struct Plan {
+  AttnParams p;
+  size_t smem_bytes;
+  int grid;
+};
+
+// Picks rows-per-item G and the K/V ring depth.  Cost model: a CTA's time is proportional to the
+// softmax slots it processes (rounds x G, G rounded up to even); a staged bias tile is amortised
+// over G streams.
+int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
+  AttnParams& p = plan->p;
+  std::memset(&p, 0, sizeof(p));
+  const int es = d.qk_dtype == AF3K_FP8_E4M3 ? 1 : 2;
+  p.B1 = (int)d.B1; p.B2 = (int)d.B2; p.Sq = (int)d.Sq; p.Sk = (int)d.Sk; p.D = (int)d.D;
+  p.n_qt = (p.Sq + kTile - 1) / kTile;
+  p.n_kt = (p.Sk + kTile - 1) / kTile;
+  p.qk_is_fp8 = es == 1;
+  p.qk_row_bytes = row_bytes_for(d.D * es);
+  p.v_row_bytes = row_bytes_for(d.D * 2);
+  p.qk_ksteps = (int)((d.D * es + 31) / 32);
+  p.nv = (int)((d.D + 15) / 16 * 16);
+  p.q_tile_bytes = kTile * p.qk_row_bytes;
+  p.k_tile_bytes = kTile * p.qk_row_bytes;
+  p.v_tile_bytes = kTile * p.v_row_bytes;
+  p.scale = d.softmax_scale;
+
+  const int budget = dev.max_smem_optin - 1024 /*alignment slack*/ - kStaticSmemReserve;
+  const int fixed = kBiasStages * kBiasTileBytes + kMaxStreams * kTile * 8 + 256 /*barriers*/;
+  const int kv_stage = (int)(p.k_tile_bytes + p.v_tile_bytes);
+  const int g_tmem = (int)((kTmemCols - 2 * kTile) / p.nv);
+  int g_max = kMaxStreams < g_tmem ? kMaxStreams : g_tmem;
+  if (g_max > p.B1) g_max = p.B1 > 0 ? p.B1 : 1;
+
+  int best_g = 0, best_stages = 0;
+  double best_cost = 0;
+  for (int g = 1; g <= g_max; ++g) {
+    if (d.rows_per_item != 0 && g != d.rows_per_item) continue;
+    int stages = (budget - fixed - g * (int)p.q_tile_bytes) / kv_stage;
+    if (stages > kMaxKvStages) stages = kMaxKvStages;
+    if (stages < 2) continue;
+    const long long groups = (p.B1 + g - 1) / g;
+    const long long items = groups * p.B2 * p.n_qt;
+    const long long rounds = (items + dev.sm_count - 1) / dev.sm_count;
+    // streams alternate between the two softmax warpgroups: an odd count leaves one idle slot
+    const int slots = (g & 1) ? g + 1 : g;
+    double cost = (double)rounds * slots * (1.0 + 0.3 / g);
+    if (stages < 3) cost *= 1.15;
+    if (best_g == 0 || cost < best_cost) { best_g = g; best_cost = cost; best_stages = stages; }
+  }
+  if (best_g == 0) return AF3K_ERR_BAD_SHAPE;
+  p.G = best_g;
+  p.kv_stages = best_stages;
+  const long long groups = (p.B1 + p.G - 1) / p.G;
+  const long long items = groups * p.B2 * p.n_qt;
+  if (items > 0x7fffffff) return AF3K_ERR_BAD_SHAPE;
+  p.n_items = (int)items;
+
+  uint32_t off = 0;
+  p.off_q = off;      off += p.G * p.q_tile_bytes;
+  p.off_kv = off;     off += p.kv_stages * kv_stage;
+  p.off_bias = off;   off += kBiasStages * kBiasTileBytes;
+  p.off_state = off;  off += kMaxStreams * kTile * 8;
+  p.off_bar = off;    off += 256;
+  size_t smem = off + 1024;
+  // One CTA per SM is required (each CTA allocates all of TMEM): ask for more than half the SM's
+  // shared memory even when the tiles need less.
+  if (smem < 120 * 1024) smem = 120 * 1024;
+  plan->smem_bytes = smem;
+  plan->grid = p.n_items < dev.sm_count ? p.n_items : dev.sm_count;
+  return AF3K_OK;
+}
+
+int encode_qkv_map(CUtensorMap* tm, const void* base, bool fp8, int64_t D, int64_t S, int64_t B2,
+                   int64_t B1, const int64_t* stride, int row_bytes) {
+  auto enc = tensor_map_encoder();
+  if (!enc) return driver_fail("cuTensorMapEncodeTiled entry point", -1);
+  const uint64_t es = fp8 ? 1 : 2;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)B2, (cuuint64_t)B1};
+  cuuint64_t strides[3] = {(cuuint64_t)stride[2] * es, (cuuint64_t)stride[1] * es,
+                           (cuuint64_t)stride[0] * es};
+  // a dimension of extent 1 may carry any stride; TMA still wants it non-zero and 16-aligned
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] == 0) strides[i] = 16;
+  cuuint32_t box[4] = {(cuuint32_t)(row_bytes / es), (cuuint32_t)kTile, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle_for(row_bytes), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? AF3K_OK : driver_fail("cuTensorMapEncodeTiled(q/k/v)", (int)r);
+}
+
+int encode_bias_map(CUtensorMap* tm, const void* base, int64_t Sk, int64_t Sq, int64_t B2,
+                    int64_t stride_h, int64_t stride_r) {
+  auto enc = tensor_map_encoder();
+  if (!enc) return driver_fail("cuTensorMapEncodeTiled entry point", -1);
+  cuuint64_t dims[3] = {(cuuint64_t)Sk, (cuuint64_t)Sq, (cuuint64_t)B2};
+  cuuint64_t strides[2] = {(cuuint64_t)stride_r * 2, (cuuint64_t)stride_h * 2};
+  for (int i = 0; i < 2; ++i)
+    if (strides[i] == 0) strides[i] = 16;
+  cuuint32_t box[3] = {64, (cuuint32_t)kTile, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? AF3K_OK : driver_fail("cuTensorMapEncodeTiled(bias)", (int)r);
+}
+
+__global__ void wait_timeout_selftest_kernel(long long limit, int* status) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    af3k::mbar_init(af3k::smem_u32(&bar), 1);
+    af3k::fence_barrier_init();
+    // nothing ever arrives on `bar`: the bounded wait must give up and report
+    const bool ok = af3k::mbar_wait_bounded(af3k::smem_u32(&bar), 0, limit, &abort_flag);
+    if (!ok && status != nullptr) atomicOr(status, (int)af3k::kStatusWaitTimeout);
+    af3k::mbar_inval(af3k::smem_u32(&bar));
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int af3k_version(void) { return 1000; }
+
+const char* af3k_strerror(int code) {
+  switch (code) {
+    case AF3K_OK: return "ok";
+    case AF3K_ERR_BAD_DTYPE: return "unsupported element type";
+    case AF3K_ERR_BAD_SHAPE: return "unsupported shape (D must be a multiple of 8 and <= 64; Sk > 0)";
+    case AF3K_ERR_BAD_STRIDE: return "unsupported stride (innermost must be 1, others 16-byte multiples)";
+    case AF3K_ERR_BAD_ALIGNMENT: return "pointer is not 16-byte aligned";
+    case AF3K_ERR_WORKSPACE: return "workspace missing or too small";
+    case AF3K_ERR_NULL_POINTER: return "null pointer";
+    case AF3K_ERR_CUDA: return "CUDA runtime or driver call failed";
+    case AF3K_ERR_UNSUPPORTED_DEVICE: return "device is not compute capability 10.x (B200)";
+    default: return "unknown error code";
+  }
+}
+
+size_t af3k_dot_product_attention_workspace(const af3k_attention_desc* desc, const void* bias) {
+  if (desc == nullptr || validate(*desc) != AF3K_OK) return 0;
+  if (!bias_needs_staging(*desc, bias)) return 0;
+  return (size_t)desc->B2 * desc->Sq * staged_bias_pitch(desc->Sk) * 2;
+}
+
+int af3k_last_launch_count(void) { return t_last_launches; }
+
+const char* af3k_last_error_detail(void) { return t_detail; }
+
+void af3k_set_wait_limit_cycles(long long cycles) { g_wait_limit.store(cycles > 0 ? cycles : -1); }
+
+int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, const void* k,
+                               const void* v, const void* bias, const uint8_t* mask, void* out,
+                               const float* q_scale, const float* k_scale, void* workspace,
+                               size_t workspace_bytes, int* status_dev, void* stream_v) {
+  t_last_launches = 0;
+  if (desc == nullptr) return AF3K_ERR_NULL_POINTER;
+  const af3k_attention_desc& d = *desc;
+  int rc = validate(d);
+  if (rc != AF3K_OK) return rc;
+  if (d.B1 == 0 || d.B2 == 0 || d.Sq == 0) return AF3K_OK;  // empty output
+  if (!q || !k || !v || !bias || !out) return AF3K_ERR_NULL_POINTER;
+  const bool fp8 = d.qk_dtype == AF3K_FP8_E4M3;
+  if (fp8 != (q_scale != nullptr) || fp8 != (k_scale != nullptr)) return AF3K_ERR_BAD_DTYPE;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return AF3K_ERR_BAD_ALIGNMENT;
+
+  DeviceInfo* dev = nullptr;
+  rc = device_info(&dev);
+  if (rc != AF3K_OK) return rc;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+
+  Plan plan;
+  rc = make_plan(d, *dev, &plan);
+  if (rc != AF3K_OK) return rc;
+  AttnParams& p = plan.p;
+  if (plan.smem_bytes > (size_t)(dev->max_smem_optin - kStaticSmemReserve)) return AF3K_ERR_BAD_SHAPE;
+
+  // bias: use in place when TMA can address it, else stage a bf16 copy in the workspace
+  const void* bias_base = bias;
+  int64_t bias_sh = d.bias_stride[0], bias_sr = d.bias_stride[1];
+  int launches = 0;
+  if (bias_needs_staging(d, bias)) {
+    const int64_t pitch = staged_bias_pitch(d.Sk);
+    const size_t need = (size_t)d.B2 * d.Sq * pitch * 2;
+    if (workspace == nullptr || workspace_bytes < need) return AF3K_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return AF3K_ERR_BAD_ALIGNMENT;
+    const long long total = (long long)d.B2 * d.Sq * (pitch / 2);
+    int blocks = (int)((total + 255) / 256);
+    if (blocks > dev->sm_count * 16) blocks = dev->sm_count * 16;
+    if (d.bias_dtype == AF3K_F32)
+      bias_to_bf16_kernel<float><<<blocks, 256, 0, stream>>>(
+          static_cast<const float*>(bias), static_cast<__nv_bfloat16*>(workspace), (int)d.B2,
+          (int)d.Sq, (int)d.Sk, d.bias_stride[0], d.bias_stride[1], (int)pitch);
+    else
+      bias_to_bf16_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+          static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(workspace),
+          (int)d.B2, (int)d.Sq, (int)d.Sk, d.bias_stride[0], d.bias_stride[1], (int)pitch);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail("launch bias_to_bf16_kernel", e);
+    ++launches;
+    bias_base = workspace;
+    bias_sr = pitch;
+    bias_sh = pitch * d.Sq;
+  }
+
+  CUtensorMap tm_q, tm_k, tm_v, tm_b;
+  if ((rc = encode_qkv_map(&tm_q, q, fp8, d.D, d.Sq, d.B2, d.B1, d.q_stride, p.qk_row_bytes))) return rc;
+  if ((rc = encode_qkv_map(&tm_k, k, fp8, d.D, d.Sk, d.B2, d.B1, d.k_stride, p.qk_row_bytes))) return rc;
+  if ((rc = encode_qkv_map(&tm_v, v, false, d.D, d.Sk, d.B2, d.B1, d.v_stride, p.v_row_bytes))) return rc;
+  if ((rc = encode_bias_map(&tm_b, bias_base, d.Sk, d.Sq, d.B2, bias_sh, bias_sr))) return rc;
+
+  p.q_scale = q_scale;
+  p.k_scale = k_scale;
+  p.mask = mask;
+  p.mask_row_stride = d.mask_row_stride;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_stride_b1 = d.out_stride[0];
+  p.out_stride_b2 = d.out_stride[1];
+  p.out_stride_s = d.out_stride[2];
+  p.status = status_dev;
+  p.wait_limit = wait_limit_cycles();
+
+  p.debug = g_debug_dump.load();
+  if (p.debug != nullptr)
+    attention_kernel<true><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
+  else
+    attention_kernel<false><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail("launch attention_kernel", e);
+  ++launches;
+  t_last_launches = launches;
+  return AF3K_OK;
+}
+
+void af3k_debug_set_dump(float* dump_dev) { g_debug_dump.store(dump_dev); }
+
+int af3k_describe_plan(const af3k_attention_desc* desc, int32_t* out6) {
+  if (desc == nullptr || out6 == nullptr) return AF3K_ERR_NULL_POINTER;
+  int rc = validate(*desc);
+  if (rc != AF3K_OK) return rc;
+  DeviceInfo dev;
+  dev.sm_count = 148;
+  dev.cc_major = 10;
+  dev.max_smem_optin = 232448;
+  int cur = 0;
+  cudaDeviceProp prop;
+  if (cudaGetDevice(&cur) == cudaSuccess && cudaGetDeviceProperties(&prop, cur) == cudaSuccess &&
+      prop.major == 10) {
+    dev.sm_count = prop.multiProcessorCount;
+    dev.max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+  }
+  Plan plan;
+  rc = make_plan(*desc, dev, &plan);
+  if (rc != AF3K_OK) return rc;
+  out6[0] = plan.p.G;
+  out6[1] = plan.p.kv_stages;
+  out6[2] = plan.p.n_items;
+  out6[3] = plan.grid;
+  out6[4] = (int32_t)plan.smem_bytes;
+  out6[5] = 2 * kTile + plan.p.G * plan.p.nv;
+  return AF3K_OK;
+}
+
+int af3k_selftest_wait_timeout(long long limit_cycles, int* status_dev, void* stream_v) {
+  if (limit_cycles <= 0) return AF3K_ERR_BAD_SHAPE;
+  wait_timeout_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(limit_cycles,
+                                                                                      status_dev);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? AF3K_OK : cuda_fail("launch wait_timeout_selftest_kernel", e);
+}
+
+}  // extern "C"

@@ -1,0 +1,561 @@
+// Biased, key-masked flash attention for sm_100a:  out = softmax(scale * Q K^T + bias, masked) V
+//
+// Replaces the per-(batch, head, 128-query block) TPP sequence of the reference
+// (src/csrc/dot_product_attention.cpp:88-122: scale -> BRGEMM -> add bias -> add mask ->
+// softmax -> BRGEMM) with one persistent warp-specialised kernel:
+//
+//   warp 0      TMA producer: Q tiles, K/V ring, bias ring (cp.async.bulk.tensor, no multicast)
+//   warp 1      tcgen05.mma issuer: S = Q K^T (smem x smem -> TMEM), O += P V (TMEM x smem -> TMEM)
+//   warp 2      TMEM allocator
+//   warps 4-7   softmax warpgroup 0 (owns S buffer 0 and the even streams of a work item)
+//   warps 8-11  softmax warpgroup 1 (owns S buffer 1 and the odd streams)
+//
+// A work item is (head, 128-query tile, group of G pair rows).  The G "streams" of an item use
+// the same bias tiles, so one staged bias tile serves G logits tiles; each stream has its own
+// Q tile, K/V tiles, fp32 running max / sum and O accumulator in TMEM.  One softmax thread owns
+// one query row (TMEM lane), so row max / row sum need no cross-thread traffic.
+//
+// Logits stay fp32 from the tensor core to the exponential; P is rounded to bf16 once, when it
+// is written back to TMEM as the A operand of the second GEMM.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "ptx_sm100.cuh"
+
+namespace af3k {
+
+constexpr int kTile = 128;         // query rows per tile == keys per tile
+constexpr int kThreads = 384;      // 12 warps
+constexpr int kMaxStreams = 8;     // pair rows per work item (TMEM: 256 + G * nv <= 512 columns)
+constexpr int kBiasStages = 2;
+constexpr int kBiasTileBytes = kTile * kTile * 2;  // bf16, two 128B-swizzled boxes of 64 columns
+constexpr int kMaxKvStages = 6;
+constexpr uint32_t kTmemCols = 512;
+// Stand-in for the reference's "-1e9" fill of masked keys.  -2^30 keeps the same meaning (weight
+// exactly 0 unless every key of the row is masked, then uniform) and its product with log2(e) is
+// exact in fp32, so a fully masked row sees exponent 0 rather than a rounding residue.
+constexpr float kMaskedLogit = -1073741824.0f;
+constexpr float kLog2e = 1.4426950408889634f;
+
+enum StatusBits : int {
+  kStatusOk = 0,
+  kStatusWaitTimeout = 1,   // a bounded mbarrier wait ran out
+};
+
+struct AttnParams {
+  int B1, B2, Sq, Sk, D;
+  int n_qt, n_kt;
+  int G;                 // streams (pair rows) per work item
+  int n_items;
+  int qk_row_bytes;      // smem bytes per Q / K tile row: 32, 64 or 128 (= swizzle span)
+  int v_row_bytes;       // same for V
+  int qk_ksteps;         // number of 32-byte K steps of the first GEMM
+  int nv;                // N of the second GEMM: D rounded up to 16
+  int kv_stages;
+  int qk_is_fp8;
+  float scale;           // softmax scale; multiplied by q_scale[h] * k_scale[h] when those are set
+  const float* q_scale;
+  const float* k_scale;
+  const uint8_t* mask;   // 1 = attend; nullptr = no mask
+  long long mask_row_stride;
+  __nv_bfloat16* out;
+  long long out_stride_b1, out_stride_b2, out_stride_s;
+  int* status;           // int[4]: {status bits, 1 + first barrier slot that timed out, block, warp}
+  long long wait_limit;  // SM clocks a single wait may take before the kernel gives up
+  float* debug;          // diagnostic dump of block 0's first logits tile (debug build of the kernel)
+  uint32_t q_tile_bytes, k_tile_bytes, v_tile_bytes;
+  uint32_t off_q, off_kv, off_bias, off_state, off_bar;   // from the 1024-aligned smem base
+};
+
+// Barrier slots inside the barrier block (8 bytes each).
+struct BarIdx {
+  static constexpr int q_full = 0, q_empty = 1, item_done = 2, epi_done = 3;
+  static constexpr int s_full = 4;      // [2]
+  static constexpr int p_ready = 6;     // [2]
+  static constexpr int bias_full = 8;   // [kBiasStages]
+  static constexpr int bias_empty = 10; // [kBiasStages]
+  static constexpr int kv_full = 12;    // [kMaxKvStages]
+  static constexpr int kv_empty = 12 + kMaxKvStages;
+  static constexpr int count = 12 + 2 * kMaxKvStages;
+};
+
+struct Ctx {
+  const AttnParams* p;
+  uint32_t smem;       // 1024-aligned shared base (shared-window address)
+  uint32_t bars;       // shared address of barrier block
+  volatile int* abort_flag;
+  uint32_t tmem;       // TMEM base address
+};
+
+__device__ __forceinline__ uint32_t bar_addr(const Ctx& c, int idx) { return c.bars + 8u * idx; }
+
+__device__ __noinline__ void report_timeout(const Ctx& c, int bar_idx) {
+  *c.abort_flag = 1;
+  if (c.p->status != nullptr) {
+    atomicOr(c.p->status, kStatusWaitTimeout);
+    if (atomicCAS(c.p->status + 1, 0, bar_idx + 1) == 0) {
+      c.p->status[2] = blockIdx.x;
+      c.p->status[3] = threadIdx.x >> 5;
+    }
+  }
+}
+
+#define AF3K_WAIT(ctx, idx, parity)                                                          \
+  do {                                                                                       \
+    if (!mbar_wait_bounded(bar_addr(ctx, idx), (parity), (ctx).p->wait_limit,                \
+                           (ctx).abort_flag)) {                                              \
+      report_timeout(ctx, idx);                                                              \
+      return;                                                                                \
+    }                                                                                        \
+  } while (0)
+
+// Warp-collective form: every lane leaves together, so no .sync.aligned instruction is ever
+// executed by part of a warp after a timeout.
+#define AF3K_WAIT_WARP(ctx, idx, parity)                                                     \
+  do {                                                                                       \
+    const bool ok_ = mbar_wait_bounded(bar_addr(ctx, idx), (parity), (ctx).p->wait_limit,    \
+                                       (ctx).abort_flag);                                    \
+    if (!__all_sync(0xffffffffu, ok_)) {                                                     \
+      report_timeout(ctx, idx);                                                                \
+      return;                                                                                \
+    }                                                                                        \
+  } while (0)
+
+__device__ __forceinline__ uint32_t swizzle_layout_code(int row_bytes) {
+  return row_bytes == 128 ? 2u : (row_bytes == 64 ? 4u : 6u);
+}
+
+struct Item {
+  int qt, h, r0, gv;
+};
+__device__ __forceinline__ Item decode_item(const AttnParams& p, int item) {
+  Item it;
+  it.qt = item % p.n_qt;
+  int t = item / p.n_qt;
+  it.h = t % p.B2;
+  int rg = t / p.B2;
+  it.r0 = rg * p.G;
+  it.gv = min(p.G, p.B1 - it.r0);
+  return it;
+}
+
+// ------------------------------------------------------------------ producer (one thread)
+__device__ void producer_role(const Ctx& c, const CUtensorMap* tm_q, const CUtensorMap* tm_k,
+                              const CUtensorMap* tm_v, const CUtensorMap* tm_bias) {
+  const AttnParams& p = *c.p;
+  uint32_t ucount = 0, bcount = 0, icount = 0;
+  const uint32_t nkv = p.kv_stages;
+  for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
+    const Item it = decode_item(p, item);
+    if (icount > 0) AF3K_WAIT(c, BarIdx::q_empty, (icount - 1) & 1);
+    mbar_arrive_expect_tx(bar_addr(c, BarIdx::q_full), it.gv * p.q_tile_bytes);
+    for (int s = 0; s < it.gv; ++s)
+      tma_load_4d(c.smem + p.off_q + s * p.q_tile_bytes, tm_q, bar_addr(c, BarIdx::q_full), 0,
+                  it.qt * kTile, it.h, it.r0 + s);
+    for (int kt = 0; kt < p.n_kt; ++kt) {
+      const uint32_t bst = bcount % kBiasStages;
+      if (bcount >= kBiasStages)
+        AF3K_WAIT(c, BarIdx::bias_empty + bst, ((bcount / kBiasStages) - 1) & 1);
+      const uint32_t bfull = bar_addr(c, BarIdx::bias_full + bst);
+      const uint32_t bdst = c.smem + p.off_bias + bst * kBiasTileBytes;
+      mbar_arrive_expect_tx(bfull, kBiasTileBytes);
+      tma_load_3d(bdst, tm_bias, bfull, kt * kTile, it.qt * kTile, it.h);
+      tma_load_3d(bdst + kBiasTileBytes / 2, tm_bias, bfull, kt * kTile + 64, it.qt * kTile, it.h);
+      ++bcount;
+      for (int s = 0; s < it.gv; ++s) {
+        const uint32_t st = ucount % nkv;
+        if (ucount >= nkv) AF3K_WAIT(c, BarIdx::kv_empty + st, ((ucount / nkv) - 1) & 1);
+        const uint32_t full = bar_addr(c, BarIdx::kv_full + st);
+        const uint32_t kdst = c.smem + p.off_kv + st * (p.k_tile_bytes + p.v_tile_bytes);
+        mbar_arrive_expect_tx(full, p.k_tile_bytes + p.v_tile_bytes);
+        tma_load_4d(kdst, tm_k, full, 0, kt * kTile, it.h, it.r0 + s);
+        tma_load_4d(kdst + p.k_tile_bytes, tm_v, full, 0, kt * kTile, it.h, it.r0 + s);
+        ++ucount;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ MMA issuer (one thread)
+struct MmaState {
+  uint32_t ucount_qk = 0, ucount_pv = 0, icount = 0;
+  uint32_t pcount[2] = {0, 0};
+};
+
+__device__ void mma_role(const Ctx& c) {
+  const AttnParams& p = *c.p;
+  const uint32_t nkv = p.kv_stages;
+  const uint32_t qk_layout = swizzle_layout_code(p.qk_row_bytes);
+  const uint32_t v_layout = swizzle_layout_code(p.v_row_bytes);
+  const uint32_t idesc_qk = make_idesc(p.qk_is_fp8 ? 0u : 1u, p.qk_is_fp8 ? 0u : 1u, 0u, 0u, kTile);
+  const uint32_t idesc_pv = make_idesc(1u, 1u, 0u, 1u, (uint32_t)p.nv);
+  const uint32_t kv_stage_bytes = p.k_tile_bytes + p.v_tile_bytes;
+  MmaState ms;
+  for (int item = blockIdx.x; item < p.n_items; item += gridDim.x) {
+    const Item it = decode_item(p, item);
+    const int gv = it.gv;
+    const int nu = p.n_kt * gv;
+    AF3K_WAIT(c, BarIdx::q_full, ms.icount & 1);
+    tc_fence_after();
+    int pv_next = 0;
+    for (int v = 0; v <= nu; ++v) {
+      // Before S buffer b is overwritten by unit v, every earlier unit that used it must have
+      // had its P*V issued (tcgen05.mma executes in issue order).  v == nu drains the rest.
+      int last = nu - 1;
+      if (v < nu) {
+        const int b = (v % gv) & 1;
+        last = -1;
+        for (int w = v - 1; w >= 0 && w >= v - gv; --w)
+          if (((w % gv) & 1) == b) { last = w; break; }
+      }
+      while (pv_next <= last) {
+        const int w = pv_next++;
+        const int s = w % gv, kt = w / gv, b = s & 1;
+        AF3K_WAIT(c, BarIdx::p_ready + b, ms.pcount[b] & 1);
+        ++ms.pcount[b];
+        if (w == 0 && ms.icount > 0) AF3K_WAIT(c, BarIdx::epi_done, (ms.icount - 1) & 1);
+        tc_fence_after();
+        const uint32_t st = ms.ucount_pv % nkv;
+        const uint32_t vbase = c.smem + p.off_kv + st * kv_stage_bytes + p.k_tile_bytes;
+        const uint32_t o_tmem = c.tmem + 2 * kTile + s * p.nv;
+        const uint32_t p_tmem = c.tmem + b * kTile;
+#pragma unroll 1
+        for (int k = 0; k < kTile / 16; ++k) {
+          const uint64_t bd = make_smem_desc(vbase + k * 16 * p.v_row_bytes, p.v_tile_bytes,
+                                             8 * p.v_row_bytes, v_layout);
+          mma_ts_f16(o_tmem, p_tmem + k * 8, bd, idesc_pv, (kt > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(bar_addr(c, BarIdx::kv_empty + st));
+        ++ms.ucount_pv;
+      }
+      if (v == nu) break;
+      const int s = v % gv, b = s & 1;
+      const uint32_t st = ms.ucount_qk % nkv;
+      AF3K_WAIT(c, BarIdx::kv_full + st, (ms.ucount_qk / nkv) & 1);
+      tc_fence_after();
+      const uint32_t qbase = c.smem + p.off_q + s * p.q_tile_bytes;
+      const uint32_t kbase = c.smem + p.off_kv + st * kv_stage_bytes;
+      const uint32_t s_tmem = c.tmem + b * kTile;
+#pragma unroll 1
+      for (int k = 0; k < p.qk_ksteps; ++k) {
+        const uint64_t ad = make_smem_desc(qbase + k * 32, 16, 8 * p.qk_row_bytes, qk_layout);
+        const uint64_t bd = make_smem_desc(kbase + k * 32, 16, 8 * p.qk_row_bytes, qk_layout);
+        if (p.qk_is_fp8) mma_ss_f8(s_tmem, ad, bd, idesc_qk, k > 0 ? 1u : 0u);
+        else             mma_ss_f16(s_tmem, ad, bd, idesc_qk, k > 0 ? 1u : 0u);
+      }
+      tc_commit(bar_addr(c, BarIdx::s_full + b));
+      ++ms.ucount_qk;
+      if (v == nu - 1) tc_commit(bar_addr(c, BarIdx::q_empty));
+    }
+    tc_commit(bar_addr(c, BarIdx::item_done));
+    ++ms.icount;
+  }
+}
+
+// ------------------------------------------------------------------ softmax
+__device__ __forceinline__ float bf16lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+
+// One 128 x 128 logits tile for one stream: the thread owns row `row` (TMEM lane).
+//   kMasked: some key of the tile is masked (mask words in mw).   kTail: keys >= nvalid do not exist.
+// mw[i] bit l  <->  key 4*l + i of the tile.
+// Diagnostic dump: four [128][128] float sections, row = query row of block 0's first tile:
+// raw logits, packed P words (64 used), un-normalised O (nv used), {running max, running sum}.
+constexpr int kDbgS = 0, kDbgP = kTile * kTile, kDbgO = 2 * kTile * kTile, kDbgML = 3 * kTile * kTile,
+              kDbgFloats = 4 * kTile * kTile;
+
+template <bool kMasked, bool kTail>
+__device__ __forceinline__ void softmax_tile(float* dbg, uint32_t s_taddr, uint32_t o_taddr, int nv,
+                                             uint32_t bias_row, uint32_t row7, float scale,
+                                             const uint32_t (&mw)[4], int nvalid, bool first_kt,
+                                             float& m_run, float& l_run) {
+  uint32_t xr[kTile];
+#pragma unroll
+  for (int cidx = 0; cidx < 4; ++cidx) tmem_ld_x32(s_taddr + cidx * 32, &xr[cidx * 32]);
+  tc_wait_ld();
+  if (dbg != nullptr) {
+#pragma unroll
+    for (int i = 0; i < kTile; ++i) dbg[kDbgS + i] = __uint_as_float(xr[i]);
+  }
+
+  float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const uint4 bv = lds128(bias_row + (j >> 3) * (kBiasTileBytes / 2) + (((j & 7) ^ row7) << 4));
+    const uint32_t w[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int col = j * 8 + e;
+      const float b = (e & 1) ? bf16hi(w[e >> 1]) : bf16lo(w[e >> 1]);
+      float x = fmaf(__uint_as_float(xr[col]), scale, b);
+      if (kMasked) {
+        const bool keep = (mw[col & 3] >> (col >> 2)) & 1u;
+        x = keep ? x : kMaskedLogit;
+      }
+      if (kTail) x = (col < nvalid) ? x : -INFINITY;
+      xr[col] = __float_as_uint(x);
+      if ((e & 3) == 0) mx0 = fmaxf(mx0, x);
+      else if ((e & 3) == 1) mx1 = fmaxf(mx1, x);
+      else if ((e & 3) == 2) mx2 = fmaxf(mx2, x);
+      else mx3 = fmaxf(mx3, x);
+    }
+  }
+  const float m_old = m_run;
+  const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m_old);
+  // exp2((m_old - m_new) * log2e): 0 on the first tile (m_old = -inf), 1 when the max stood still
+  const float alpha = ex2_approx((m_old - m_new) * kLog2e);
+
+  if (!first_kt) {
+    if (__any_sync(0xffffffffu, m_new > m_old)) {
+      for (int c0 = 0; c0 < nv; c0 += 16) {
+        uint32_t o[16];
+        tmem_ld_x16(o_taddr + c0, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st_x16(o_taddr + c0, o);
+      }
+    }
+  }
+
+  const float neg_mc = -m_new * kLog2e;
+  float sm0 = 0.f, sm1 = 0.f, sm2 = 0.f, sm3 = 0.f;
+#pragma unroll
+  for (int cidx = 0; cidx < 8; ++cidx) {
+    uint32_t pk[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int col = cidx * 16 + 2 * i;
+      const float p0 = ex2_approx(fmaf(__uint_as_float(xr[col]), kLog2e, neg_mc));
+      const float p1 = ex2_approx(fmaf(__uint_as_float(xr[col + 1]), kLog2e, neg_mc));
+      if (i & 1) { sm2 += p0; sm3 += p1; } else { sm0 += p0; sm1 += p1; }
+      pk[i] = pack_bf16x2(p0, p1);
+    }
+    if (dbg != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dbg[kDbgP + cidx * 8 + i] = __uint_as_float(pk[i]);
+    }
+    // P (bf16, two keys per 32-bit column) overwrites the first 64 columns of the S buffer
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
+                 ::"r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
+                 "r"(pk[6]), "r"(pk[7]), "r"(s_taddr + cidx * 8)
+                 : "memory");
+  }
+  tc_wait_st();
+  m_run = m_new;
+  l_run = l_run * alpha + ((sm0 + sm1) + (sm2 + sm3));
+}
+
+template <bool kDebug>
+__device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
+  const AttnParams& p = *c.p;
+  const int row = wq * 32 + lane;                    // row of the 128-query tile == TMEM lane
+  const uint32_t lane_sel = (uint32_t)(wq * 32) << 16;
+  const uint32_t s_taddr = c.tmem + lane_sel + wg * kTile;
+  float* st_m = reinterpret_cast<float*>(__cvta_shared_to_generic(c.smem + p.off_state));
+  float* st_l = st_m + kMaxStreams * kTile;
+  uint32_t scnt = 0, bcount = 0, icount = 0;
+  const int tail_keys = p.Sk - (p.n_kt - 1) * kTile;   // keys present in the last key tile
+
+  for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
+    const Item it = decode_item(p, item);
+    float scale = p.scale;
+    if (p.q_scale != nullptr) scale *= p.q_scale[it.h] * p.k_scale[it.h];
+
+    for (int kt = 0; kt < p.n_kt; ++kt) {
+      const uint32_t bst = bcount % kBiasStages;
+      AF3K_WAIT_WARP(c, BarIdx::bias_full + bst, (bcount / kBiasStages) & 1);
+      const uint32_t bias_row = c.smem + p.off_bias + bst * kBiasTileBytes + row * 128;
+      const bool is_tail = (kt == p.n_kt - 1) && (tail_keys != kTile);
+
+      for (int s = wg; s < it.gv; s += 2) {
+        // key-mask bits of this (pair row, key tile): lane l fetches keys 4l .. 4l+3
+        uint32_t mw[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+        if (p.mask != nullptr) {
+          const uint8_t* mrow = p.mask + (long long)(it.r0 + s) * p.mask_row_stride;
+          const int k0 = kt * kTile + 4 * lane;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const bool keep = (k0 + i < p.Sk) ? (mrow[k0 + i] != 0) : true;
+            mw[i] = __ballot_sync(0xffffffffu, keep);
+          }
+        }
+        const bool all_keep = (mw[0] & mw[1] & mw[2] & mw[3]) == 0xffffffffu;
+
+        float m_run = -INFINITY, l_run = 0.f;
+        if (kt > 0) { m_run = st_m[s * kTile + row]; l_run = st_l[s * kTile + row]; }
+
+        AF3K_WAIT_WARP(c, BarIdx::s_full + wg, scnt & 1);
+        ++scnt;
+        tc_fence_after();
+        const uint32_t o_taddr = c.tmem + lane_sel + 2 * kTile + s * p.nv;
+        float* dbg = nullptr;
+        if (kDebug && p.debug != nullptr && blockIdx.x == 0 && icount == 0 && s == 0 && kt == 0)
+          dbg = p.debug + (size_t)row * kTile;
+        if (is_tail)
+          softmax_tile<true, true>(dbg, s_taddr, o_taddr, p.nv, bias_row, row & 7, scale, mw, tail_keys,
+                                   kt == 0, m_run, l_run);
+        else if (!all_keep)
+          softmax_tile<true, false>(dbg, s_taddr, o_taddr, p.nv, bias_row, row & 7, scale, mw, kTile,
+                                    kt == 0, m_run, l_run);
+        else
+          softmax_tile<false, false>(dbg, s_taddr, o_taddr, p.nv, bias_row, row & 7, scale, mw, kTile,
+                                     kt == 0, m_run, l_run);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::p_ready + wg));
+        st_m[s * kTile + row] = m_run;
+        st_l[s * kTile + row] = l_run;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::bias_empty + bst));
+      ++bcount;
+    }
+
+    // ---- epilogue: O / l -> bf16 -> global
+    AF3K_WAIT_WARP(c, BarIdx::item_done, icount & 1);
+    tc_fence_after();
+    const int qrow = it.qt * kTile + row;
+    for (int s = wg; s < it.gv; s += 2) {
+      const float inv = 1.0f / st_l[s * kTile + row];
+      const uint32_t o_taddr = c.tmem + lane_sel + 2 * kTile + s * p.nv;
+      __nv_bfloat16* orow = p.out + (long long)(it.r0 + s) * p.out_stride_b1 +
+                            (long long)it.h * p.out_stride_b2 + (long long)qrow * p.out_stride_s;
+      for (int c0 = 0; c0 < p.nv; c0 += 16) {
+        uint32_t o[16];
+        tmem_ld_x16(o_taddr + c0, o);
+        tc_wait_ld();
+        if (kDebug && p.debug != nullptr && blockIdx.x == 0 && icount == 0 && s == 0) {
+          float* dbg = p.debug + (size_t)row * kTile;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) dbg[kDbgO + c0 + i] = __uint_as_float(o[i]);
+          dbg[kDbgML + 0] = st_m[s * kTile + row];
+          dbg[kDbgML + 1] = st_l[s * kTile + row];
+        }
+        if (qrow < p.Sq) {
+#pragma unroll
+          for (int hseg = 0; hseg < 2; ++hseg) {
+            if (c0 + hseg * 8 + 8 <= p.D) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(o[hseg * 8 + 0]) * inv, __uint_as_float(o[hseg * 8 + 1]) * inv);
+              v.y = pack_bf16x2(__uint_as_float(o[hseg * 8 + 2]) * inv, __uint_as_float(o[hseg * 8 + 3]) * inv);
+              v.z = pack_bf16x2(__uint_as_float(o[hseg * 8 + 4]) * inv, __uint_as_float(o[hseg * 8 + 5]) * inv);
+              v.w = pack_bf16x2(__uint_as_float(o[hseg * 8 + 6]) * inv, __uint_as_float(o[hseg * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + c0 + hseg * 8) = v;
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::epi_done));
+  }
+}
+
+// ------------------------------------------------------------------ kernel
+template <bool kDebug>
+__global__ void __launch_bounds__(kThreads, 1)
+attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ CUtensorMap tm_q,
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                 const __grid_constant__ CUtensorMap tm_bias) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  Ctx c;
+  c.p = &p;
+  c.smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  c.bars = c.smem + p.off_bar;
+  c.abort_flag = &abort_flag;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_v);
+    prefetch_tensormap(&tm_bias);
+    mbar_init(bar_addr(c, BarIdx::q_full), 1);
+    mbar_init(bar_addr(c, BarIdx::q_empty), 1);
+    mbar_init(bar_addr(c, BarIdx::item_done), 1);
+    mbar_init(bar_addr(c, BarIdx::epi_done), 8);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_addr(c, BarIdx::s_full + i), 1);
+      mbar_init(bar_addr(c, BarIdx::p_ready + i), 4);
+    }
+    for (int i = 0; i < kBiasStages; ++i) {
+      mbar_init(bar_addr(c, BarIdx::bias_full + i), 1);
+      mbar_init(bar_addr(c, BarIdx::bias_empty + i), 8);
+    }
+    for (int i = 0; i < kMaxKvStages; ++i) {
+      mbar_init(bar_addr(c, BarIdx::kv_full + i), 1);
+      mbar_init(bar_addr(c, BarIdx::kv_empty + i), 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  c.tmem = tmem_base_slot;
+
+  if (warp == 0) {
+    if (lane == 0) producer_role(c, &tm_q, &tm_k, &tm_v, &tm_bias);
+  } else if (warp == 1) {
+    if (lane == 0) mma_role(c);
+  } else if (warp >= 4) {
+    softmax_role<kDebug>(c, (warp - 4) >> 2, warp & 3, lane);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag != 0) {
+    // a wait ran out: give loads and MMAs still in flight time to land before smem / TMEM go away
+    for (int i = 0; i < 200; ++i) __nanosleep(10000);
+    __syncthreads();
+  }
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(c.tmem, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ bias staging pre-pass
+// bias (fp32 or bf16, arbitrary row pitch) -> bf16 [B2, Sq, pitch] with a TMA-legal pitch.
+template <typename T>
+__global__ void bias_to_bf16_kernel(const T* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                    int B2, int Sq, int Sk, long long src_stride_h,
+                                    long long src_stride_r, int pitch) {
+  const long long total = (long long)B2 * Sq * (pitch / 2);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int cp = (int)(i % (pitch / 2));
+    const long long t = i / (pitch / 2);
+    const int r = (int)(t % Sq);
+    const int h = (int)(t / Sq);
+    const T* s = src + h * src_stride_h + r * src_stride_r;
+    const int col = cp * 2;
+    const float a = col < Sk ? (float)s[col] : 0.f;
+    const float b = col + 1 < Sk ? (float)s[col + 1] : 0.f;
+    reinterpret_cast<uint32_t*>(dst)[i] = pack_bf16x2(a, b);
+  }
+}
+
+}  // namespace af3k

@@ -1,0 +1,134 @@
+"""Row-sharded attention over the GPUs of one node.
+
+Every (pair row, head) is an independent attention problem, so the rows of the pair
+representation are split into contiguous blocks, one per rank, exactly as the reference's
+``DistributedGridSelfAttentionCpp`` does (src/af3_kernels/Attention.py:145-156): rank ``r`` owns
+rows ``[r * ceil(rows / ws), (r + 1) * ceil(rows / ws))``; the bias is replicated and the mask is
+sliced by row.  No collective sits on the data path of the kernel.  The optional output
+all-gather is cut into ``comm_split`` pieces and issued on a side stream, so the gather of piece
+``i`` overlaps the kernel of piece ``i + 1`` (the reference does this with a helper thread and a
+queue, Attention.py:162-195).
+"""
+from __future__ import annotations
+
+import time
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .tools import pad_to_size, record_comm_time
+
+
+def row_partition(rows: int, world_size: int, rank: int) -> Tuple[int, int, int]:
+    """-> (begin, end, split_size): the row block of ``rank`` and the padded block size."""
+    if world_size <= 0 or not (0 <= rank < world_size):
+        raise ValueError("bad world_size / rank")
+    split = (rows + world_size - 1) // world_size
+    begin = min(rows, split * rank)
+    end = min(rows, begin + split)
+    return begin, end, split
+
+
+class RowShardedAttention:
+    """Shards ``dot_product_attention`` by pair row over a process group.
+
+    ``attention_fn(q, k, v, mask, bias) -> out`` defaults to the CUDA operator; tests running on
+    CPU ranks (gloo) pass a stand-in so that the partition / gather logic is exercised without a GPU.
+    """
+
+    def __init__(self, group=None, comm_split: int = 4, attention_fn: Optional[Callable] = None):
+        if comm_split < 1:
+            raise ValueError("comm_split must be >= 1")
+        self.group = group
+        self.comm_split = comm_split
+        if attention_fn is None:
+            from .dpa import dot_product_attention as attention_fn
+        self.attention_fn = attention_fn
+        self._comm_stream = None
+
+    # ------------------------------------------------------------------ helpers
+    @property
+    def world_size(self) -> int:
+        return dist.get_world_size(self.group)
+
+    @property
+    def rank(self) -> int:
+        return dist.get_rank(self.group)
+
+    def broadcast_shared(self, bias: torch.Tensor, mask: Optional[torch.Tensor], src: int = 0):
+        """Broadcasts the replicated operands (bias, full mask) once from ``src`` into each
+        rank's own memory.  Returns the work handles' results already waited on."""
+        dist.broadcast(bias, src=src, group=self.group)
+        if mask is not None:
+            m = mask.view(torch.uint8) if mask.dtype == torch.bool else mask
+            dist.broadcast(m, src=src, group=self.group)
+        return bias, mask
+
+    def shard(self, full: torch.Tensor, rows: int) -> torch.Tensor:
+        """This rank's contiguous row block of a tensor whose first dimension is the pair row."""
+        b, e, _ = row_partition(rows, self.world_size, self.rank)
+        return full[b:e]
+
+    # ------------------------------------------------------------------ compute
+    def forward_local(self, q, k, v, mask, bias) -> torch.Tensor:
+        """Attention over this rank's rows only; the output stays row-sharded."""
+        return self.attention_fn(q, k, v, mask, bias)
+
+    def forward(self, q, k, v, mask, bias, rows: int, timeout_s: float = 60.0) -> torch.Tensor:
+        """q, k, v, mask: this rank's row block (``shard`` of the full tensors).  Returns the
+        full ``[rows, H, N, D]`` output on every rank."""
+        ws, rank = self.world_size, self.rank
+        b, e, split = row_partition(rows, ws, rank)
+        local_rows = e - b
+        if q.shape[0] != local_rows:
+            raise ValueError(f"rank {rank} expected {local_rows} local rows, got {q.shape[0]}")
+        _, H, N, D = q.shape
+        piece = (split + self.comm_split - 1) // self.comm_split
+        out_dtype = torch.bfloat16 if q.is_cuda else q.dtype
+        full = torch.empty((ws, split, H, N, D), dtype=out_dtype, device=q.device)
+
+        use_streams = q.is_cuda
+        if use_streams and self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=q.device)
+        works = []
+        t0 = time.time()
+        for p0 in range(0, split, piece):
+            p1 = min(split, p0 + piece)
+            lo, hi = min(p0, local_rows), min(p1, local_rows)
+            if hi > lo:
+                m = None
+                if mask is not None:
+                    m = mask[lo:hi] if mask.dim() >= 2 and mask.shape[0] == local_rows else mask
+                o = self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias)
+                o = pad_to_size(o, p1 - p0, 0)
+            else:  # this rank's block ends before the piece: contribute zero rows
+                o = torch.zeros((p1 - p0, H, N, D), dtype=out_dtype, device=q.device)
+            buf = torch.empty((ws, p1 - p0, H, N, D), dtype=out_dtype, device=q.device)
+            if use_streams:
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream(q.device))
+                with torch.cuda.stream(self._comm_stream):
+                    self._comm_stream.wait_event(ev)
+                    dist.all_gather_into_tensor(buf.view(-1, H, N, D), o, group=self.group)
+                    full[:, p0:p1].copy_(buf)
+                    o.record_stream(self._comm_stream)
+                    buf.record_stream(self._comm_stream)
+            else:
+                w = dist.all_gather_into_tensor(buf.view(-1, H, N, D), o, group=self.group,
+                                                async_op=True)
+                works.append((w, buf, p0, p1))
+        for w, buf, p0, p1 in works:
+            if not w.wait(timeout=_timedelta(timeout_s)):
+                raise RuntimeError("all_gather did not complete")
+            full[:, p0:p1].copy_(buf)
+        if use_streams:
+            torch.cuda.current_stream(q.device).wait_stream(self._comm_stream)
+        record_comm_time("AG Attn", time.time() - t0, full.numel() * full.element_size())
+        return full.view(ws * split, H, N, D)[:rows]
+
+
+def _timedelta(seconds: float):
+    import datetime
+
+    return datetime.timedelta(seconds=seconds)

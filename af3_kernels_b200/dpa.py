@@ -1,0 +1,171 @@
+"""Host side of the biased, key-masked attention operator.
+
+Mirrors what the reference does between its Python wrapper and its C++ entry
+(src/af3_kernels/__init__.py:31-52 -> src/csrc/dot_product_attention.cpp:545-559): rank-lifts
+the mask, checks dtypes and shapes, allocates the output, and calls the C ABI of libaf3k.so
+with raw device pointers on the current CUDA stream.  There is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from typing import Optional
+
+import torch
+
+from . import _capi
+
+_DEBUG = os.environ.get("AF3K_DEBUG", "0") == "1"
+_status_buffers: dict = {}
+
+
+def _status_buffer(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index)
+    buf = _status_buffers.get(key)
+    if buf is None:
+        buf = torch.zeros(4, dtype=torch.int32, device=device)
+        _status_buffers[key] = buf
+    return buf
+
+
+def read_status(device: torch.device) -> list:
+    """Synchronises and returns the device status words {bits, 1+barrier, block, warp}; clears them."""
+    buf = _status_buffer(torch.device(device))
+    vals = buf.cpu().tolist()
+    buf.zero_()
+    return vals
+
+
+def _mask_rows(mask: Optional[torch.Tensor], B1: int, Sk: int):
+    """-> (uint8 tensor [rows, Sk] with unit inner stride, row stride in bytes) or (None, 0).
+
+    1-D [Sk] broadcasts over the batch; 2-D is [B1, Sk]; higher ranks must be [B1|1, 1, 1, Sk]
+    (what the reference builds at src/af3_kernels/__init__.py:41-44).  True / non-zero = attend.
+    """
+    if mask is None:
+        return None, 0
+    if mask.dim() == 0:
+        raise ValueError("mask must have at least one dimension")
+    if mask.dim() >= 3:
+        if mask.shape[-1] != Sk or mask.numel() not in (Sk, B1 * Sk):
+            raise ValueError(f"mask of shape {tuple(mask.shape)} is not [B1|1, 1, 1, Sk]")
+        mask = mask.reshape(-1, Sk)
+    if mask.dim() == 1:
+        mask = mask[None, :]
+    if mask.shape[-1] != Sk or mask.shape[0] not in (1, B1):
+        raise ValueError(f"mask of shape {tuple(mask.shape)} does not match B1={B1}, Sk={Sk}")
+    if mask.dtype != torch.bool:
+        mask = mask != 0
+    mask = mask.contiguous().view(torch.uint8)
+    stride = 0 if (mask.shape[0] == 1 and B1 != 1) else Sk
+    return mask, stride
+
+
+def dot_product_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    mask: Optional[torch.Tensor],
+    bias: torch.Tensor,
+    *,
+    q_scale: Optional[torch.Tensor] = None,
+    k_scale: Optional[torch.Tensor] = None,
+    softmax_scale: Optional[float] = None,
+    rows_per_item: int = 0,
+    out: Optional[torch.Tensor] = None,
+    check_status: Optional[bool] = None,
+) -> torch.Tensor:
+    """softmax(scale * q k^T + bias, key-masked) v on the current CUDA stream.
+
+    q, k, v: [B1, B2, S, D] on one CUDA device.  q/k bf16, or float8_e4m3fn with per-head fp32
+    ``q_scale`` / ``k_scale`` [B2].  v bf16.  bias: B2*Sq*Sk elements, bf16 or fp32, shared by
+    every b1.  mask: see ``_mask_rows``.  Returns a new bf16 tensor; inputs are not modified.
+    """
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("q, k, v must be 4-D [B1, B2, S, D]")
+    if not q.is_cuda:
+        raise RuntimeError("af3_kernels_b200 runs on CUDA tensors only (no CPU fallback)")
+    if k.device != q.device or v.device != q.device or bias.device != q.device:
+        raise ValueError("q, k, v, bias must live on the same device")
+    B1, B2, Sq, D = q.shape
+    Sk = k.shape[2]
+    if k.shape != (B1, B2, Sk, D) or v.shape != (B1, B2, Sk, D):
+        raise ValueError("k and v must be [B1, B2, Sk, D] matching q")
+    fp8 = q.dtype == torch.float8_e4m3fn
+    if fp8:
+        if k.dtype != torch.float8_e4m3fn or q_scale is None or k_scale is None:
+            raise TypeError("fp8 q needs fp8 k and q_scale / k_scale")
+        q_scale = q_scale.to(device=q.device, dtype=torch.float32).contiguous()
+        k_scale = k_scale.to(device=q.device, dtype=torch.float32).contiguous()
+        if q_scale.numel() != B2 or k_scale.numel() != B2:
+            raise ValueError("q_scale / k_scale must have one entry per head")
+    else:
+        if q.dtype != torch.bfloat16:
+            raise TypeError(f"q must be bfloat16 or float8_e4m3fn, got {q.dtype}")
+        if q_scale is not None or k_scale is not None:
+            raise TypeError("q_scale / k_scale are only valid with fp8 q and k")
+        if k.dtype != torch.bfloat16:
+            k = k.to(torch.bfloat16)
+    if v.dtype != torch.bfloat16:
+        v = v.to(torch.bfloat16)
+    if bias.numel() != B2 * Sq * Sk:
+        raise ValueError(f"bias must have B2*Sq*Sk = {B2 * Sq * Sk} elements, got {bias.numel()}")
+    if bias.dtype not in (torch.bfloat16, torch.float32):
+        bias = bias.to(torch.float32)
+    bias = bias.reshape(B2, Sq, Sk) if bias.dim() != 3 else bias
+    if Sk > 1 and bias.stride(2) != 1:
+        bias = bias.contiguous()
+
+    def _inner_contig(t):
+        return t if (t.stride(3) == 1 or t.shape[3] == 1) else t.contiguous()
+
+    q, k, v = _inner_contig(q), _inner_contig(k), _inner_contig(v)
+    mask_u8, mask_stride = _mask_rows(mask, B1, Sk)
+    if mask_u8 is not None and mask_u8.device != q.device:
+        mask_u8 = mask_u8.to(q.device)
+
+    if out is None:
+        out = torch.empty((B1, B2, Sq, D), dtype=torch.bfloat16, device=q.device)
+    elif out.shape != (B1, B2, Sq, D) or out.dtype != torch.bfloat16 or out.stride(3) != 1:
+        raise ValueError("out must be a bf16 [B1, B2, Sq, D] tensor with unit inner stride")
+    if out.numel() == 0:
+        return out
+
+    desc = _capi.AttentionDesc()
+    desc.B1, desc.B2, desc.Sq, desc.Sk, desc.D = B1, B2, Sq, Sk, D
+    for name, t in (("q_stride", q), ("k_stride", k), ("v_stride", v), ("out_stride", out)):
+        getattr(desc, name)[:] = [t.stride(0), t.stride(1), t.stride(2)]
+    desc.bias_stride[:] = [bias.stride(0), bias.stride(1)]
+    desc.mask_row_stride = mask_stride
+    desc.qk_dtype = _capi.AF3K_FP8_E4M3 if fp8 else _capi.AF3K_BF16
+    desc.bias_dtype = _capi.AF3K_BF16 if bias.dtype == torch.bfloat16 else _capi.AF3K_F32
+    desc.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    desc.rows_per_item = int(rows_per_item)
+
+    lib = _capi.load()
+    with torch.cuda.device(q.device):
+        ws_bytes = lib.af3k_dot_product_attention_workspace(ctypes.byref(desc), bias.data_ptr())
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
+        status = _status_buffer(q.device)
+        code = lib.af3k_dot_product_attention(
+            ctypes.byref(desc),
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), bias.data_ptr(),
+            mask_u8.data_ptr() if mask_u8 is not None else None,
+            out.data_ptr(),
+            q_scale.data_ptr() if fp8 else None,
+            k_scale.data_ptr() if fp8 else None,
+            ws.data_ptr() if ws is not None else None,
+            ws_bytes,
+            status.data_ptr(),
+            torch.cuda.current_stream().cuda_stream,
+        )
+        _capi.check(code)
+        if check_status if check_status is not None else _DEBUG:
+            st = read_status(q.device)
+            if st[0] != 0:
+                raise RuntimeError(
+                    f"af3k kernel reported status {st[0]} (wait timeout: barrier slot {st[1] - 1}, "
+                    f"block {st[2]}, warp {st[3]})"
+                )
+    return out

@@ -1,0 +1,128 @@
+/* C ABI of the B200 (sm_100a) attention library  libaf3k.so.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless stated otherwise.  The
+ * library borrows all buffers, owns nothing, writes only `out`, `workspace` and `status_dev`,
+ * and launches on the stream it is given without synchronising.
+ *
+ * Each entry point names the reference interface it stands in for (paths are those of the
+ * HPC-SJTU/af3_kernels source tree).
+ */
+#ifndef AF3K_H_
+#define AF3K_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* return codes (0 = ok).  af3k_strerror() gives the text. */
+enum {
+  AF3K_OK = 0,
+  AF3K_ERR_BAD_DTYPE = 1,
+  AF3K_ERR_BAD_SHAPE = 2,
+  AF3K_ERR_BAD_STRIDE = 3,
+  AF3K_ERR_BAD_ALIGNMENT = 4,
+  AF3K_ERR_WORKSPACE = 5,
+  AF3K_ERR_NULL_POINTER = 6,
+  AF3K_ERR_CUDA = 7,
+  AF3K_ERR_UNSUPPORTED_DEVICE = 8
+};
+
+/* element types */
+enum {
+  AF3K_BF16 = 0,
+  AF3K_F32 = 1,
+  AF3K_FP8_E4M3 = 2
+};
+
+/* bits of the device status word written by the kernels (0 = clean run) */
+enum {
+  AF3K_STATUS_WAIT_TIMEOUT = 1 /* a bounded on-device wait ran out; output is not valid */
+};
+
+/* Shapes, strides (in ELEMENTS) and types of one attention call.
+ *   q, k, v, out : [B1, B2, S, D]   innermost (D) stride must be 1
+ *   bias         : [B2, Sq, Sk]     shared by every b1; innermost stride must be 1
+ *   mask         : [B1, Sk] bytes, non-zero = attend; row stride 0 broadcasts one row
+ * D must be a multiple of 8 and at most 64.  q/k may be bf16 or fp8-e4m3 (then q_scale/k_scale
+ * hold one fp32 de-quantisation factor per head); v and out are bf16; bias is bf16 or fp32.
+ */
+typedef struct af3k_attention_desc {
+  int64_t B1, B2, Sq, Sk, D;
+  int64_t q_stride[3];    /* b1, b2, s */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t out_stride[3];
+  int64_t bias_stride[2]; /* head, query row */
+  int64_t mask_row_stride;
+  int32_t qk_dtype;       /* AF3K_BF16 or AF3K_FP8_E4M3 */
+  int32_t bias_dtype;     /* AF3K_BF16 or AF3K_F32 */
+  float softmax_scale;    /* the reference uses 1/sqrt(D) */
+  int32_t rows_per_item;  /* 0 = choose; else pair rows that share one staged bias tile (1..8) */
+} af3k_attention_desc;
+
+/* Library / ABI version (major * 1000 + minor). */
+int af3k_version(void);
+
+/* Text for a return code.  Never NULL. */
+const char* af3k_strerror(int code);
+
+/* For AF3K_ERR_CUDA: which CUDA call failed on this thread and the runtime's text for it
+ * ("" if none failed yet).  Never NULL. */
+const char* af3k_last_error_detail(void);
+
+/* Bytes of device scratch af3k_dot_product_attention needs for this problem (0 if none):
+ * the bf16 staging copy of a bias that is fp32 or whose row pitch TMA cannot address. */
+size_t af3k_dot_product_attention_workspace(const af3k_attention_desc* desc, const void* bias);
+
+/* out = softmax(scale * q k^T + bias, key-masked) v
+ *
+ * Stands in for  at::Tensor dot_product_attention(q, k, v, mask, bias, use_flash_attention,
+ * BLK_SZ, FLASH_SZ)  (src/csrc/dot_product_attention.h:25-32, bound at src/csrc/init.cpp:349-351)
+ * and the work its Python wrapper does before it (src/af3_kernels/__init__.py:41-50).
+ * Differences a caller sees: inputs are never written (the reference overwrites q), the result
+ * goes to a caller-provided `out`, masked keys are a byte predicate instead of an additive
+ * -1e9 tensor, and errors come back as codes instead of exit(1).
+ *
+ * mask may be NULL (no key is masked).  q_scale / k_scale must be NULL for bf16 q/k.
+ * status_dev may be NULL; otherwise it must point at int[4] the caller zeroed: [0] is OR-ed
+ * with AF3K_STATUS_* bits by the device, [1..3] identify the first wait that gave up
+ * (1 + barrier slot, block, warp).  stream is a cudaStream_t.
+ */
+int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, const void* k,
+                               const void* v, const void* bias, const uint8_t* mask, void* out,
+                               const float* q_scale, const float* k_scale, void* workspace,
+                               size_t workspace_bytes, int* status_dev, void* stream);
+
+/* Number of kernels the last successful af3k_dot_product_attention call on this thread
+ * launched (1, or 2 when the bias staging pre-pass ran). */
+int af3k_last_launch_count(void);
+
+/* Upper bound, in SM clock cycles, for any single on-device wait (default 2e9, about a second).
+ * A kernel whose wait runs out sets AF3K_STATUS_WAIT_TIMEOUT and returns. */
+void af3k_set_wait_limit_cycles(long long cycles);
+
+/* Launch plan the library would use for `desc` on the current device (a B200 with 148 SMs and
+ * 227 KB of shared memory per block is assumed when no such device is present, so this also
+ * works on a CPU-only host): out6 = {pair rows per work item, K/V ring stages, work items,
+ * grid size, dynamic shared memory bytes, TMEM columns used}.  Diagnostic; no counterpart in
+ * the reference. */
+int af3k_describe_plan(const af3k_attention_desc* desc, int32_t* out6);
+
+/* Diagnostic: when dump_dev is non-NULL, later attention calls run a debug build of the kernel
+ * that writes block 0's first logits tile to dump_dev (4 * 128 * 128 floats: raw logits, packed
+ * P words, un-normalised O, {max, sum}).  Pass NULL to switch it off.  No counterpart in the
+ * reference. */
+void af3k_debug_set_dump(float* dump_dev);
+
+/* Self-test of the bounded wait: launches one block that waits, with the given limit, on a
+ * barrier nothing ever arrives at, and writes AF3K_STATUS_WAIT_TIMEOUT to status_dev when the
+ * wait gives up.  No counterpart in the reference (it has no device code). */
+int af3k_selftest_wait_timeout(long long limit_cycles, int* status_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AF3K_H_ */
