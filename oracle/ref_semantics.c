@@ -27,9 +27,16 @@
  * 0 selects the float instantiation (no intermediate rounding).
  */
 #include <math.h>
+#include <pthread.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#include <unistd.h>
+
+int af3k_oracle_num_threads(void) {
+  long n = sysconf(_SC_NPROCESSORS_ONLN);
+  return n > 0 ? (int)n : 1;
+}
 
 static inline float bf16_round(float f) {
   uint32_t u;
@@ -143,62 +150,82 @@ static void task_flash(const float* q, const float* k, const float* v, const flo
   free(cur);
 }
 
-/* Returns 0 on success.  mask_row_stride = 0 broadcasts one mask row over B1. */
+/* ---- task pool: the reference runs "#pragma omp parallel for collapse(3)" over (batch, head,
+ * query block) (:88); gcc's OpenMP runtime is not installed in this image, so the same task
+ * list is handed out to pthreads through an atomic counter. */
+typedef struct {
+  const float *q, *k, *v, *bias;
+  const uint8_t* keep;
+  long mask_row_stride;
+  float* out;
+  int B1, B2, S, K, M, Mb, BLK, FLASH, flash, rb;
+  int next_task; /* atomic */
+  int failed;
+} job_t;
+
+static void* worker(void* arg) {
+  job_t* J = (job_t*)arg;
+  float* L = (float*)malloc(sizeof(float) * (size_t)J->BLK * (J->flash ? J->FLASH : J->M));
+  float* qs = (float*)malloc(sizeof(float) * (size_t)J->BLK * J->K);
+  float* maskadd = (float*)malloc(sizeof(float) * (size_t)J->M);
+  if (!L || !qs || !maskadd) {
+    __atomic_store_n(&J->failed, 1, __ATOMIC_RELAXED);
+  } else {
+    const float neg = rnd(-1e9f, J->rb);
+    const int ntasks = J->B1 * J->B2 * J->Mb;
+    for (;;) {
+      const int t = __atomic_fetch_add(&J->next_task, 1, __ATOMIC_RELAXED);
+      if (t >= ntasks) break;
+      const int kb = t % J->Mb, j = (t / J->Mb) % J->B2, i = t / (J->Mb * J->B2);
+      /* mask: 1.0 = masked, padded keys are masked (:54), times T(-1e9) (:63-74) */
+      for (int c = 0; c < J->M; ++c) {
+        const int masked =
+            (c >= J->S) || (J->keep && !J->keep[(size_t)i * J->mask_row_stride + c]);
+        maskadd[c] = rnd((masked ? 1.0f : 0.0f) * neg, J->rb);
+      }
+      const size_t off = ((size_t)i * J->B2 + j) * (size_t)J->S * J->K;
+      const float* bj = J->bias + (size_t)j * J->S * J->S;
+      if (J->flash)
+        task_flash(J->q + off, J->k + off, J->v + off, bj, maskadd, J->out + off, J->S, J->K,
+                   J->M, J->BLK, J->FLASH, kb, J->rb, L, qs);
+      else
+        task_plain(J->q + off, J->k + off, J->v + off, bj, maskadd, J->out + off, J->S, J->K,
+                   J->M, J->BLK, kb, J->rb, L, qs);
+    }
+  }
+  free(L);
+  free(qs);
+  free(maskadd);
+  return NULL;
+}
+
+/* Returns 0 on success.  mask_row_stride = 0 broadcasts one mask row over B1.
+ * num_threads <= 0 uses every online CPU. */
 int af3k_oracle_dot_product_attention(const float* q, const float* k, const float* v,
                                       const float* bias, const uint8_t* keep,
                                       long mask_row_stride, float* out, int B1, int B2, int S,
                                       int K, int BLK_SZ, int use_flash, int FLASH_SZ,
-                                      int round_bf16) {
+                                      int round_bf16, int num_threads) {
   if (B1 <= 0 || B2 <= 0 || S <= 0 || K <= 0 || BLK_SZ <= 0 || FLASH_SZ <= 0) return 1;
-  const int M = (S + BLK_SZ - 1) / BLK_SZ * BLK_SZ; /* :45 keys padded to a block multiple */
-  const int Mb = M / BLK_SZ;
-  const int flash = use_flash && M > FLASH_SZ;       /* :76 */
-  const int rb = round_bf16;
-  const float neg = rnd(-1e9f, rb);
-  int failed = 0;
-#pragma omp parallel
-  {
-    float* L = (float*)malloc(sizeof(float) * (size_t)BLK_SZ * (flash ? FLASH_SZ : M));
-    float* qs = (float*)malloc(sizeof(float) * (size_t)BLK_SZ * K);
-    float* maskadd = (float*)malloc(sizeof(float) * (size_t)M);
-    if (!L || !qs || !maskadd) {
-#pragma omp atomic write
-      failed = 1;
-    } else {
-#pragma omp for collapse(3) schedule(dynamic, 1)
-      for (int i = 0; i < B1; ++i)
-        for (int j = 0; j < B2; ++j)
-          for (int kb = 0; kb < Mb; ++kb) {
-            /* mask: 1.0 = masked, padded keys are masked (:54), times T(-1e9) (:63-74) */
-            for (int c = 0; c < M; ++c) {
-              const int masked = (c >= S) || (keep && !keep[(size_t)i * mask_row_stride + c]);
-              maskadd[c] = rnd((masked ? 1.0f : 0.0f) * neg, rb);
-            }
-            const size_t off = ((size_t)i * B2 + j) * (size_t)S * K;
-            const float* bj = bias + (size_t)j * S * S;
-            if (flash)
-              task_flash(q + off, k + off, v + off, bj, maskadd, out + off, S, K, M, BLK_SZ,
-                         FLASH_SZ, kb, rb, L, qs);
-            else
-              task_plain(q + off, k + off, v + off, bj, maskadd, out + off, S, K, M, BLK_SZ, kb,
-                         rb, L, qs);
-          }
-    }
-    free(L);
-    free(qs);
-    free(maskadd);
-  }
-  return failed;
-}
-
-int af3k_oracle_num_threads(void) {
-  int n = 1;
-#ifdef _OPENMP
-#pragma omp parallel
-  {
-#pragma omp master
-    n = omp_get_num_threads();
-  }
-#endif
-  return n;
+  job_t J;
+  J.q = q; J.k = k; J.v = v; J.bias = bias; J.keep = keep;
+  J.mask_row_stride = mask_row_stride;
+  J.out = out;
+  J.B1 = B1; J.B2 = B2; J.S = S; J.K = K;
+  J.M = (S + BLK_SZ - 1) / BLK_SZ * BLK_SZ; /* :45 keys padded to a block multiple */
+  J.Mb = J.M / BLK_SZ;
+  J.BLK = BLK_SZ; J.FLASH = FLASH_SZ;
+  J.flash = use_flash && J.M > FLASH_SZ;    /* :76 */
+  J.rb = round_bf16;
+  J.next_task = 0;
+  J.failed = 0;
+  int nt = num_threads > 0 ? num_threads : af3k_oracle_num_threads();
+  if (nt > 256) nt = 256;
+  pthread_t th[256];
+  int started = 0;
+  for (int t = 0; t < nt - 1; ++t)
+    if (pthread_create(&th[started], NULL, worker, &J) == 0) ++started;
+  worker(&J);
+  for (int t = 0; t < started; ++t) pthread_join(th[t], NULL);
+  return J.failed;
 }

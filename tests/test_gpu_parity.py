@@ -1,0 +1,276 @@
+"""Parity of the CUDA path (called through the C ABI of libaf3k.so) against the CPU oracles.
+
+Tolerances are those of the path's specification, measured against the fp32 oracle on the same
+stored inputs: bf16 max-abs <= 2e-2 and mean-abs <= 2e-3; fp8 (e4m3 q/k, de-quantised oracle)
+max-abs <= 6e-2.
+"""
+import ctypes
+import math
+
+import pytest
+import torch
+
+import af3_kernels_b200 as A
+from af3_kernels_b200 import _capi
+from af3_kernels_b200.dpa import dot_product_attention, read_status
+from oracle import attention_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+BF16_MAX_ABS, BF16_MEAN_ABS = 2e-2, 2e-3
+FP8_MAX_ABS = 6e-2
+
+
+def _to(dev, *ts):
+    return [t.to(dev) if t is not None else None for t in ts]
+
+
+def _run(dev, q, k, v, mask, bias, **kw):
+    qd, kd, vd, md, bd = _to(dev, q, k, v, mask, bias)
+    for name in ("q_scale", "k_scale"):
+        if kw.get(name) is not None:
+            kw[name] = kw[name].to(dev)
+    out = dot_product_attention(qd, kd, vd, md, bd, check_status=True, **kw)
+    return out.cpu()
+
+
+def _check_bf16(out, ref, what):
+    st = O.error_stats(out, ref)
+    assert st["nan"] == 0, (what, st)
+    assert st["max_abs"] <= BF16_MAX_ABS and st["mean_abs"] <= BF16_MEAN_ABS, (what, st)
+    return st
+
+
+def test_loaded_library_is_the_cuda_one(cuda_device):
+    lib = _capi.load()
+    assert lib.af3k_version() >= 1000
+    assert torch.cuda.get_device_capability(cuda_device)[0] == 10
+
+
+def test_golden_vectors(cuda_device, golden):
+    for name, c in golden.items():
+        out = _run(cuda_device, c["q"], c["k"], c["v"], c["mask"], c["bias"])
+        _check_bf16(out, c["ref_fp32"], name)
+        if not name.startswith("fully_masked"):
+            # against the restatement of the reference's own bf16 rounding scheme: both sit
+            # within their own distance of the fp32 result
+            o2 = O.ref_semantics(c["q"], c["k"], c["v"], c["mask"], c["bias"])
+            st = O.error_stats(out, o2)
+            assert st["max_abs"] <= 6e-2 + BF16_MAX_ABS and st["mean_abs"] <= 3e-3 + BF16_MEAN_ABS, (name, st)
+
+
+@pytest.mark.parametrize("name", ["cfg1", "cfg3", "cfg4"])
+def test_benchmark_configs_full_size(cuda_device, name):
+    inp = O.make_inputs(name)
+    out = _run(cuda_device, inp["q"], inp["k"], inp["v"], inp["mask"], inp["bias"])
+    ref = O.oracle_fp32(inp["q"], inp["k"], inp["v"], inp["mask"], inp["bias"])
+    _check_bf16(out, ref, name)
+
+
+def test_cfg2_reduced_rows_against_oracle(cuda_device):
+    inp = O.make_inputs("cfg2", rows=24)
+    out = _run(cuda_device, inp["q"], inp["k"], inp["v"], inp["mask"], inp["bias"])
+    ref = O.oracle_fp32(inp["q"], inp["k"], inp["v"], inp["mask"], inp["bias"])
+    _check_bf16(out, ref, "cfg2 rows=24")
+
+
+def test_cfg2_full_size_properties(cuda_device):
+    dev = cuda_device
+    g = torch.Generator(device=dev).manual_seed(0)
+    B1, B2, S, D = 768, 4, 768, 32
+    q = torch.randn(B1, B2, S, D, generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn(B1, B2, S, D, generator=g, device=dev).to(torch.bfloat16)
+    v = torch.randn(B1, B2, S, D, generator=g, device=dev).to(torch.bfloat16)
+    bias = torch.randn(B2, S, S, generator=g, device=dev)
+    mask = torch.rand(B1, S, generator=g, device=dev) >= 0.05
+    q0 = q.clone()
+    out = dot_product_attention(q, k, v, mask, bias, check_status=True)
+    assert torch.equal(q, q0), "inputs must not be written"
+    # (1) bit-reproducible
+    again = dot_product_attention(q, k, v, mask, bias, check_status=True)
+    assert torch.equal(out, again)
+    # (2) rows are independent problems: a slice of the rows gives the same bits
+    rows = torch.tensor([0, 5, 383, 767], device=dev)
+    sub = dot_product_attention(q[rows], k[rows], v[rows], mask[rows], bias, check_status=True)
+    assert torch.equal(sub, out[rows])
+    # (3) the slice against the CPU oracle
+    ref = O.oracle_fp32(q[rows].cpu(), k[rows].cpu(), v[rows].cpu(), mask[rows].cpu(), bias.cpu())
+    _check_bf16(sub.cpu(), ref, "cfg2 full, row subset")
+    # (4) softmax weights sum to one: V = 1 gives 1 everywhere
+    ones = dot_product_attention(q, k, torch.ones_like(v), mask, bias, check_status=True)
+    assert (ones.float() - 1.0).abs().max().item() <= 1e-2
+
+
+def test_cfg5_fp8_reduced_rows(cuda_device):
+    inp = O.make_inputs("cfg5", rows=6)
+    out = _run(cuda_device, inp["q"], inp["k"], inp["v"], inp["mask"], inp["bias"],
+               q_scale=inp["q_scale"], k_scale=inp["k_scale"])
+    ref = O.oracle_fp32(inp["q"], inp["k"], inp["v"], inp["mask"], inp["bias"],
+                        q_scale=inp["q_scale"], k_scale=inp["k_scale"])
+    st = O.error_stats(out, ref)
+    assert st["nan"] == 0 and st["max_abs"] <= FP8_MAX_ABS, st
+
+
+def test_cfg5_fp8_quarter_size_properties(cuda_device):
+    dev = cuda_device
+    g = torch.Generator(device=dev).manual_seed(0)
+    B1, B2, S, D = 512, 4, 2048, 32
+    qf = torch.randn(B1, B2, S, D, generator=g, device=dev)
+    kf = torch.randn(B1, B2, S, D, generator=g, device=dev)
+    v = torch.randn(B1, B2, S, D, generator=g, device=dev).to(torch.bfloat16)
+    bias = torch.randn(B2, S, S, generator=g, device=dev).to(torch.bfloat16)
+    mask = torch.rand(B1, S, generator=g, device=dev) >= 0.05
+    q, qs = O.quantize_e4m3_per_head(qf)
+    k, ks = O.quantize_e4m3_per_head(kf)
+    del qf, kf
+    out = dot_product_attention(q, k, v, mask, bias, q_scale=qs, k_scale=ks, check_status=True)
+    again = dot_product_attention(q, k, v, mask, bias, q_scale=qs, k_scale=ks, check_status=True)
+    assert torch.equal(out, again)
+    rows = torch.tensor([0, 255, 511], device=dev)
+    ref = O.oracle_fp32(q[rows].cpu(), k[rows].cpu(), v[rows].cpu(), mask[rows].cpu(), bias.cpu(),
+                        q_scale=qs.cpu(), k_scale=ks.cpu())
+    st = O.error_stats(out[rows].cpu(), ref)
+    assert st["nan"] == 0 and st["max_abs"] <= FP8_MAX_ABS, st
+
+
+@pytest.mark.parametrize("S", [1, 17, 127, 128, 129, 257])
+@pytest.mark.parametrize("D", [24, 32, 48])
+def test_odd_sequence_lengths(cuda_device, S, D):
+    g = torch.Generator().manual_seed(S * 100 + D)
+    B1, B2 = 3, 2
+    q = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    bias = torch.randn(B2, S, S, generator=g)
+    mask = torch.rand(B1, S, generator=g) >= 0.2
+    mask[:, 0] = True
+    out = _run(cuda_device, q, k, v, mask, bias)
+    _check_bf16(out, O.oracle_fp32(q, k, v, mask, bias), (S, D))
+
+
+@pytest.mark.parametrize("D", [8, 16, 40, 56, 64])
+def test_other_head_dims(cuda_device, D):
+    g = torch.Generator().manual_seed(D)
+    q = torch.randn(2, 3, 200, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(2, 3, 200, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(2, 3, 200, D, generator=g).to(torch.bfloat16)
+    bias = torch.randn(3, 200, 200, generator=g).to(torch.bfloat16)
+    out = _run(cuda_device, q, k, v, None, bias)
+    _check_bf16(out, O.oracle_fp32(q, k, v, None, bias), D)
+
+
+def test_mask_and_bias_forms(cuda_device):
+    g = torch.Generator().manual_seed(3)
+    B1, B2, S, D = 4, 2, 150, 32
+    q = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    bias = torch.randn(B2, S, S, generator=g)
+    m1 = torch.rand(S, generator=g) >= 0.3
+    m2 = m1[None, :].expand(B1, S).contiguous()
+    ref = O.oracle_fp32(q, k, v, m2, bias)
+    o1 = _run(cuda_device, q, k, v, m1, bias)                       # 1-D broadcasts over the batch
+    o2 = _run(cuda_device, q, k, v, m2, bias)                       # 2-D
+    o4 = _run(cuda_device, q, k, v, m2[:, None, None, :], bias)     # what the reference builds
+    ob = _run(cuda_device, q, k, v, m2, bias[None])                 # 4-D bias [1, H, S, S]
+    _check_bf16(o1, ref, "1-D mask")
+    assert torch.equal(o1, o2) and torch.equal(o2, o4) and torch.equal(o2, ob)
+    onone = _run(cuda_device, q, k, v, None, bias)
+    _check_bf16(onone, O.oracle_fp32(q, k, v, None, bias), "no mask")
+
+
+def test_fully_masked_row_is_uniform_over_real_keys(cuda_device):
+    g = torch.Generator().manual_seed(4)
+    B1, B2, S, D = 2, 2, 200, 32
+    q = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    bias = torch.randn(B2, S, S, generator=g)
+    mask = torch.rand(B1, S, generator=g) >= 0.1
+    mask[0, :] = False
+    out = _run(cuda_device, q, k, v, mask, bias)
+    _check_bf16(out, O.oracle_fp32(q, k, v, mask, bias), "fully masked row")
+    uniform = v[0].float().mean(dim=1, keepdim=True).expand(B2, S, D)
+    assert (out[0].float() - uniform).abs().max().item() <= 1e-2
+
+
+def test_rows_per_item_choices_give_identical_bits(cuda_device):
+    g = torch.Generator().manual_seed(5)
+    B1, B2, S, D = 11, 2, 300, 32
+    q = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    bias = torch.randn(B2, S, S, generator=g).to(torch.bfloat16)
+    mask = torch.rand(B1, S, generator=g) >= 0.05
+    base = _run(cuda_device, q, k, v, mask, bias, rows_per_item=1)
+    _check_bf16(base, O.oracle_fp32(q, k, v, mask, bias), "G=1")
+    for G in range(2, 9):
+        assert torch.equal(_run(cuda_device, q, k, v, mask, bias, rows_per_item=G), base), G
+
+
+def test_strided_inputs_and_output(cuda_device):
+    dev = cuda_device
+    g = torch.Generator().manual_seed(6)
+    B1, B2, S, D = 2, 4, 130, 32
+    # [B, S, H, D] projections viewed as [B, H, S, D]: the usual layout after a fused QKV linear
+    qkv = torch.randn(3, B1, S, B2, D, generator=g).to(torch.bfloat16).to(dev)
+    q, k, v = (t.permute(0, 2, 1, 3) for t in qkv)
+    assert not q.is_contiguous()
+    bias = torch.randn(B2, S, S, generator=g).to(dev)
+    mask = (torch.rand(B1, S, generator=g) >= 0.1).to(dev)
+    out = dot_product_attention(q, k, v, mask, bias, check_status=True)
+    ref = O.oracle_fp32(q.cpu(), k.cpu(), v.cpu(), mask.cpu(), bias.cpu())
+    _check_bf16(out.cpu(), ref, "strided")
+    dst = torch.zeros(B1, S, B2, D, dtype=torch.bfloat16, device=dev).permute(0, 2, 1, 3)
+    dot_product_attention(q, k, v, mask, bias, out=dst, check_status=True)
+    assert torch.equal(dst, out)
+
+
+def test_output_padding_is_not_overwritten(cuda_device):
+    dev = cuda_device
+    g = torch.Generator().manual_seed(8)
+    B1, B2, S, D = 2, 2, 77, 24
+    q = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16).to(dev)
+    bias = torch.randn(B2, S, S, generator=g).to(dev)
+    big = torch.full((B1, B2, S + 2, D + 8), 7.0, dtype=torch.bfloat16, device=dev)
+    view = big[:, :, 1:S + 1, :D]
+    dot_product_attention(q, q, q, None, bias, out=view, check_status=True)
+    assert (big[:, :, 0] == 7).all() and (big[:, :, S + 1] == 7).all() and (big[..., D:] == 7).all()
+    assert not (view == 7).all()
+
+
+def test_reference_named_wrapper_and_dtype_checks(cuda_device):
+    dev = cuda_device
+    q = torch.randn(1, 2, 64, 32, device=dev).to(torch.bfloat16)
+    bias = torch.zeros(2, 64, 64, device=dev)
+    mask = torch.ones(64, dtype=torch.bool, device=dev)
+    out = A.dot_product_attention_cpp(q, q, q, mask, bias, True, 64, 256)   # knobs accepted, ignored
+    assert out.shape == q.shape and out.dtype == torch.bfloat16
+    with pytest.raises(TypeError):
+        A.dot_product_attention_cpp(q.half(), q.half(), q.half(), mask, bias)
+    with pytest.raises(ValueError):
+        A.dot_product_attention_cpp(q, q, q, mask, bias[:, :32])
+    empty = A.dot_product_attention_cpp(q[:0], q[:0], q[:0], mask, bias)
+    assert empty.shape == (0, 2, 64, 32)
+
+
+def test_bounded_wait_reports_instead_of_hanging(cuda_device):
+    lib = _capi.load()
+    st = torch.zeros(4, dtype=torch.int32, device=cuda_device)
+    assert lib.af3k_selftest_wait_timeout(5_000_000, st.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert st[0].item() == _capi.AF3K_STATUS_WAIT_TIMEOUT
+    # the context is still usable afterwards
+    q = torch.randn(1, 1, 32, 32, device=cuda_device).to(torch.bfloat16)
+    out = dot_product_attention(q, q, q, None, torch.zeros(1, 32, 32, device=cuda_device), check_status=True)
+    assert torch.isfinite(out.float()).all()
+
+
+def test_launch_count(cuda_device):
+    lib = _capi.load()
+    q = torch.randn(1, 1, 64, 32, device=cuda_device).to(torch.bfloat16)
+    dot_product_attention(q, q, q, None, torch.zeros(1, 64, 64, device=cuda_device))
+    assert lib.af3k_last_launch_count() == 2          # fp32 bias: staging pre-pass + attention
+    dot_product_attention(q, q, q, None, torch.zeros(1, 64, 64, device=cuda_device, dtype=torch.bfloat16))
+    assert lib.af3k_last_launch_count() == 1
+    assert read_status(cuda_device)[0] == 0
