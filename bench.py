@@ -46,7 +46,7 @@ def load_peaks():
 class ClockSampler:
     """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.004):
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
         self.max_mhz = None
@@ -178,12 +178,14 @@ def workload_config(name, c, world, sample_rows=None):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--rows", type=int, default=0, help="override pair rows per GPU (debugging)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="only warm-up + timed steps with a bf16 bias (for ncu captures): no e2e, no CPU leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -255,6 +257,8 @@ def main():
         torch.cuda.synchronize()
 
     lib = _capi.load()
+    if args.kernel_only:
+        bias = bias.to(torch.bfloat16)
     for _ in range(args.warmup):
         step()
     launches_per_step = lib.af3k_last_launch_count()
@@ -280,6 +284,17 @@ def main():
 
     flops_rank = O.attention_flops(B1, B2, S, S, D)
     value = world * flops_rank / (ms_per_step / 1e3) / 1e12
+
+    if args.kernel_only:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+                              "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                              "kernel_only": True, "config": workload_config(name, c, world),
+                              "device_status": status}), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     # ---- end to end through the reference-facing operator with HOST buffers (every rank)
     host = {n: t.cpu().pin_memory() for n, t in (("q", q), ("k", k), ("v", v), ("bias", bias), ("mask", mask))}
