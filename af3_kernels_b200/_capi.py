@@ -23,6 +23,8 @@ EXPORTED_SYMBOLS = (
     "af3k_last_error_detail",
     "af3k_dot_product_attention_workspace",
     "af3k_dot_product_attention",
+    "af3k_dot_product_attention_noalloc",
+    "af3k_static_scratch_bytes",
     "af3k_last_launch_count",
     "af3k_set_wait_limit_cycles",
     "af3k_describe_plan",
@@ -85,6 +87,10 @@ def load() -> ctypes.CDLL:
     lib.af3k_dot_product_attention_workspace.argtypes = [dp, vp]
     lib.af3k_dot_product_attention.restype = ctypes.c_int
     lib.af3k_dot_product_attention.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp, vp]
+    lib.af3k_dot_product_attention_noalloc.restype = ctypes.c_int
+    lib.af3k_dot_product_attention_noalloc.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.af3k_static_scratch_bytes.restype = sz
+    lib.af3k_static_scratch_bytes.argtypes = []
     lib.af3k_last_launch_count.restype = ctypes.c_int
     lib.af3k_last_launch_count.argtypes = []
     lib.af3k_set_wait_limit_cycles.restype = None

@@ -261,6 +261,38 @@ __global__ void wait_timeout_selftest_kernel(long long limit, int* status) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Variant for callers that have no way to hand us scratch memory.
+//
+// The bf16 staging copy of the bias normally lives in a caller-provided workspace.  Some hosts
+// cannot provide one: a serving process that gave every byte of device memory to its own arena
+// at start-up, a plug-in interface that only passes inputs and outputs through, or a
+// latency-critical loop in which cudaMalloc (which synchronises the device) is forbidden.  For
+// them the staging copy goes into a fixed array that is part of this library's device image.
+// The array is reserved on every GPU that loads the library, for the life of the process, so
+// its size is kept modest.
+constexpr size_t kStaticScratchBytes = 16u << 20;   // 16 MiB: B2 * Sq * round_up(Sk, 8) <= 8 Mi entries
+static __device__ __align__(256) unsigned char g_static_bias_scratch[kStaticScratchBytes];
+
+// In host code the name of a __device__ array is only a handle for the runtime, not an address
+// the GPU can use; the real device address has to be asked for, per device.
+int static_scratch_address(void** out) {
+  static void* addr[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) return cuda_fail("cudaGetDevice", e);
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_bias_scratch);   // resolves for the current device
+    if (e != cudaSuccess || p == nullptr) return cuda_fail("cudaGetSymbolAddress(static scratch)", e);
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return AF3K_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -278,6 +310,7 @@ const char* af3k_strerror(int code) {
     case AF3K_ERR_NULL_POINTER: return "null pointer";
     case AF3K_ERR_CUDA: return "CUDA runtime or driver call failed";
     case AF3K_ERR_UNSUPPORTED_DEVICE: return "device is not compute capability 10.x (B200)";
+    case AF3K_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the built-in array holds";
     default: return "unknown error code";
   }
 }
@@ -404,6 +437,31 @@ int af3k_describe_plan(const af3k_attention_desc* desc, int32_t* out6) {
   out6[4] = (int32_t)plan.smem_bytes;
   out6[5] = 2 * kTile + plan.p.G * plan.p.nv;
   return AF3K_OK;
+}
+
+size_t af3k_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int af3k_dot_product_attention_noalloc(const af3k_attention_desc* desc, const void* q,
+                                       const void* k, const void* v, const void* bias,
+                                       const uint8_t* mask, void* out, const float* q_scale,
+                                       const float* k_scale, int* status_dev, void* stream) {
+  if (desc == nullptr) return AF3K_ERR_NULL_POINTER;
+  int rc = validate(*desc);
+  if (rc != AF3K_OK) return rc;
+  const size_t need = af3k_dot_product_attention_workspace(desc, bias);
+  if (need > kStaticScratchBytes) {
+    std::snprintf(t_detail, sizeof(t_detail),
+                  "bias staging copy needs %zu bytes, the built-in scratch holds %zu", need,
+                  kStaticScratchBytes);
+    return AF3K_ERR_SCRATCH_LIMIT;
+  }
+  void* scratch = nullptr;
+  if (need != 0 && (rc = static_scratch_address(&scratch)) != AF3K_OK) return rc;
+  // From here on this is the ordinary call with the built-in array as its workspace.  The
+  // staging pre-pass rewrites every entry it later reads (pad columns included), so nothing of a
+  // previous call's contents needs clearing.
+  return af3k_dot_product_attention(desc, q, k, v, bias, mask, out, q_scale, k_scale, scratch,
+                                    need != 0 ? kStaticScratchBytes : 0, status_dev, stream);
 }
 
 int af3k_selftest_wait_timeout(long long limit_cycles, int* status_dev, void* stream_v) {

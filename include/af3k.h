@@ -27,7 +27,8 @@ enum {
   AF3K_ERR_WORKSPACE = 5,
   AF3K_ERR_NULL_POINTER = 6,
   AF3K_ERR_CUDA = 7,
-  AF3K_ERR_UNSUPPORTED_DEVICE = 8
+  AF3K_ERR_UNSUPPORTED_DEVICE = 8,
+  AF3K_ERR_SCRATCH_LIMIT = 9
 };
 
 /* element types */
@@ -95,6 +96,32 @@ int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, c
                                const void* v, const void* bias, const uint8_t* mask, void* out,
                                const float* q_scale, const float* k_scale, void* workspace,
                                size_t workspace_bytes, int* status_dev, void* stream);
+
+/* The same operation for callers that cannot supply a workspace and cannot allocate one: a
+ * host that handed all device memory to its own arena at start-up, a plug-in boundary that only
+ * carries inputs and outputs, or a serving loop where cudaMalloc (which synchronises the whole
+ * device) is not allowed.  This entry point has no counterpart in the reference.
+ *
+ * It makes no cudaMalloc / cudaFree call and uses no allocating library routine.  The bias
+ * staging copy goes into an array of af3k_static_scratch_bytes() (16 MiB) that is built into the
+ * library's device image, so every GPU that loads the library gives up that much memory until
+ * the process exits.  A problem whose staging copy is larger (B2 * Sq * round_up(Sk, 8) * 2
+ * bytes; none is needed for a bf16 bias with 16-byte-aligned rows) is refused with
+ * AF3K_ERR_SCRATCH_LIMIT and nothing is launched.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current); make that first call outside any stream capture.  All calls on a device
+ * share the one array: two calls whose kernels can overlap on the GPU (different streams) race
+ * on it, so keep them on one stream or order them with events.  Nothing in the array has to be
+ * cleared between calls; each call rewrites every entry it reads.
+ * Arguments are those of af3k_dot_product_attention without the workspace pair. */
+int af3k_dot_product_attention_noalloc(const af3k_attention_desc* desc, const void* q,
+                                       const void* k, const void* v, const void* bias,
+                                       const uint8_t* mask, void* out, const float* q_scale,
+                                       const float* k_scale, int* status_dev, void* stream);
+
+/* Size in bytes of the built-in scratch array used by af3k_dot_product_attention_noalloc. */
+size_t af3k_static_scratch_bytes(void);
 
 /* Number of kernels the last successful af3k_dot_product_attention call on this thread
  * launched (1, or 2 when the bias staging pre-pass ran). */

@@ -36,7 +36,7 @@ def test_version_and_strerror():
     lib = _capi.load()
     assert lib.af3k_version() >= 1000
     assert lib.af3k_strerror(0) == b"ok"
-    for code in range(1, 9):
+    for code in range(1, 10):
         assert lib.af3k_strerror(code) not in (b"", b"ok", b"unknown error code")
     assert lib.af3k_strerror(999) == b"unknown error code"
 
