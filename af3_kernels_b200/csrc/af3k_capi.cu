@@ -168,14 +168,16 @@ int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
   const int budget = dev.max_smem_optin - 1024 /*alignment slack*/ - kStaticSmemReserve;
   const int fixed = kBiasStages * kBiasTileBytes + kMaxStreams * kTile * 8 + 256 /*barriers*/;
   const int kv_stage = (int)(p.k_tile_bytes + p.v_tile_bytes);
-  const int g_tmem = (int)((kTmemCols - 2 * kTile) / p.nv);
+  const int g_tmem = (int)((kTmemCols - kOCol) / p.nv);
   int g_max = kMaxStreams < g_tmem ? kMaxStreams : g_tmem;
   if (g_max > p.B1) g_max = p.B1 > 0 ? p.B1 : 1;
 
   int best_g = 0, best_stages = 0;
   double best_cost = 0;
+  // rows_per_item is a request: it is honoured up to what TMEM and the batch allow
+  const int g_req = d.rows_per_item > g_max ? g_max : d.rows_per_item;
   for (int g = 1; g <= g_max; ++g) {
-    if (d.rows_per_item != 0 && g != d.rows_per_item) continue;
+    if (g_req != 0 && g != g_req) continue;
     int stages = (budget - fixed - g * (int)p.q_tile_bytes) / kv_stage;
     if (stages > kMaxKvStages) stages = kMaxKvStages;
     if (stages < 2) continue;
@@ -435,7 +437,7 @@ int af3k_describe_plan(const af3k_attention_desc* desc, int32_t* out6) {
   out6[2] = plan.p.n_items;
   out6[3] = plan.grid;
   out6[4] = (int32_t)plan.smem_bytes;
-  out6[5] = 2 * kTile + plan.p.G * plan.p.nv;
+  out6[5] = (int32_t)kOCol + plan.p.G * plan.p.nv;
   return AF3K_OK;
 }
 

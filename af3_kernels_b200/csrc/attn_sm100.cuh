@@ -7,8 +7,8 @@
 //   warp 0      TMA producer: Q tiles, K/V ring, bias ring (cp.async.bulk.tensor, no multicast)
 //   warp 1      tcgen05.mma issuer: S = Q K^T (smem x smem -> TMEM), O += P V (TMEM x smem -> TMEM)
 //   warp 2      TMEM allocator
-//   warps 4-7   softmax warpgroup 0 (owns S buffer 0 and the even streams of a work item)
-//   warps 8-11  softmax warpgroup 1 (owns S buffer 1 and the odd streams)
+//   warps 4-7   softmax warpgroup 0 (owns S / P buffer 0 and the even streams of a work item)
+//   warps 8-11  softmax warpgroup 1 (owns S / P buffer 1 and the odd streams)
 //
 // A work item is (head, 128-query tile, group of G pair rows).  The G "streams" of an item use
 // the same bias tiles, so one staged bias tile serves G logits tiles; each stream has its own
@@ -16,7 +16,10 @@
 // one query row (TMEM lane), so row max / row sum need no cross-thread traffic.
 //
 // Logits stay fp32 from the tensor core to the exponential; P is rounded to bf16 once, when it
-// is written back to TMEM as the A operand of the second GEMM.
+// is written to TMEM as the A operand of the second GEMM.  S and P live in separate TMEM columns:
+// a warpgroup releases its S buffer as soon as the logits are in registers, so the next Q K^T of
+// that buffer runs under the softmax of the current tile.  O is rescaled lazily: only when a row
+// maximum grows by more than 2^8 (exact, because l is scaled with it).
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -29,7 +32,12 @@ namespace af3k {
 
 constexpr int kTile = 128;         // query rows per tile == keys per tile
 constexpr int kThreads = 384;      // 12 warps
-constexpr int kMaxStreams = 8;     // pair rows per work item (TMEM: 256 + G * nv <= 512 columns)
+// 65536 registers per SM: launched at 168 per thread, then 128 x 56 + 256 x 224 = 64512
+constexpr int kRegsMisc = 56, kRegsSoftmax = 224;
+constexpr int kMaxStreams = 8;     // pair rows per work item (TMEM: kOCol + G * nv <= 512 columns)
+// TMEM columns: two fp32 logits buffers, two bf16 P buffers (two keys per column), then O.
+constexpr uint32_t kSCol = 0, kPCol = 2 * 128, kOCol = 2 * 128 + 2 * 64;
+constexpr float kLazyRescaleLog2 = 8.0f;   // keep a stale row max while exp2 arguments stay <= 8
 constexpr int kBiasStages = 2;
 constexpr int kBiasTileBytes = kTile * kTile * 2;  // bf16, two 128B-swizzled boxes of 64 columns
 constexpr int kMaxKvStages = 6;
@@ -73,13 +81,15 @@ struct AttnParams {
 // Barrier slots inside the barrier block (8 bytes each).
 struct BarIdx {
   static constexpr int q_full = 0, q_empty = 1, item_done = 2, epi_done = 3;
-  static constexpr int s_full = 4;      // [2]
-  static constexpr int p_ready = 6;     // [2]
-  static constexpr int bias_full = 8;   // [kBiasStages]
-  static constexpr int bias_empty = 10; // [kBiasStages]
-  static constexpr int kv_full = 12;    // [kMaxKvStages]
-  static constexpr int kv_empty = 12 + kMaxKvStages;
-  static constexpr int count = 12 + 2 * kMaxKvStages;
+  static constexpr int s_full = 4;      // [2]  Q K^T of a tile finished
+  static constexpr int s_free = 6;      // [2]  softmax warpgroup has the logits in registers
+  static constexpr int p_ready = 8;     // [2]  P written (and O rescaled if needed)
+  static constexpr int pv_done = 10;    // [2]  P V of a tile finished: P buffer and O are free
+  static constexpr int bias_full = 12;  // [kBiasStages]
+  static constexpr int bias_empty = 14; // [kBiasStages]
+  static constexpr int kv_full = 16;    // [kMaxKvStages]
+  static constexpr int kv_empty = 16 + kMaxKvStages;
+  static constexpr int count = 16 + 2 * kMaxKvStages;
 };
 
 struct Ctx {
@@ -180,11 +190,9 @@ __device__ void producer_role(const Ctx& c, const CUtensorMap* tm_q, const CUten
 }
 
 // ------------------------------------------------------------------ MMA issuer (one thread)
-struct MmaState {
-  uint32_t ucount_qk = 0, ucount_pv = 0, icount = 0;
-  uint32_t pcount[2] = {0, 0};
-};
-
+// Event loop: a Q K^T is issued as soon as its S buffer was released and its K/V stage landed, a
+// P V as soon as its P was written.  Both conditions are polled without blocking, so neither can
+// starve the other whatever the number of streams per item.
 __device__ void mma_role(const Ctx& c) {
   const AttnParams& p = *c.p;
   const uint32_t nkv = p.kv_stages;
@@ -193,72 +201,104 @@ __device__ void mma_role(const Ctx& c) {
   const uint32_t idesc_qk = make_idesc(p.qk_is_fp8 ? 0u : 1u, p.qk_is_fp8 ? 0u : 1u, 0u, 0u, kTile);
   const uint32_t idesc_pv = make_idesc(1u, 1u, 0u, 1u, (uint32_t)p.nv);
   const uint32_t kv_stage_bytes = p.k_tile_bytes + p.v_tile_bytes;
-  MmaState ms;
-  for (int item = blockIdx.x; item < p.n_items; item += gridDim.x) {
+  // descriptor words for tile 0 / stage 0; later tiles only move the start-address field
+  const uint64_t qd0 = make_smem_desc(c.smem + p.off_q, 16, 8 * p.qk_row_bytes, qk_layout);
+  const uint64_t kd0 = make_smem_desc(c.smem + p.off_kv, 16, 8 * p.qk_row_bytes, qk_layout);
+  const uint64_t vd0 = make_smem_desc(c.smem + p.off_kv + p.k_tile_bytes, p.v_tile_bytes,
+                                      8 * p.v_row_bytes, v_layout);
+  const uint32_t qd_lo = (uint32_t)qd0, qd_hi = (uint32_t)(qd0 >> 32);
+  const uint32_t kd_lo = (uint32_t)kd0, kd_hi = (uint32_t)(kd0 >> 32);
+  const uint32_t vd_lo = (uint32_t)vd0, vd_hi = (uint32_t)(vd0 >> 32);
+  const uint32_t q_step = p.q_tile_bytes >> 4, stage_step = kv_stage_bytes >> 4;
+  const uint32_t v_kstep = (16u * p.v_row_bytes) >> 4;
+  const int ksteps = p.qk_ksteps;
+  const bool fp8 = p.qk_is_fp8 != 0;
+  // ring positions / barrier parities are carried incrementally: no division on this thread
+  uint32_t qk_st = 0, qk_par = 0, pv_st = 0;           // K/V stage of the next QK / PV, kv_full parity
+  uint32_t icount = 0;
+  uint32_t sfree_par0 = 0, sfree_par1 = 0;             // parity of the s_free phase the next QK needs
+  uint32_t qk_first0 = 1, qk_first1 = 1;               // no tile issued on the buffer yet
+  uint32_t pready_par0 = 0, pready_par1 = 0;
+  for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
     const Item it = decode_item(p, item);
     const int gv = it.gv;
     const int nu = p.n_kt * gv;
-    AF3K_WAIT(c, BarIdx::q_full, ms.icount & 1);
+    AF3K_WAIT(c, BarIdx::q_full, icount & 1);
     tc_fence_after();
-    int pv_next = 0;
-    for (int v = 0; v <= nu; ++v) {
-      // Before S buffer b is overwritten by unit v, every earlier unit that used it must have
-      // had its P*V issued (tcgen05.mma executes in issue order).  v == nu drains the rest.
-      int last = nu - 1;
-      if (v < nu) {
-        const int b = (v % gv) & 1;
-        last = -1;
-        for (int w = v - 1; w >= 0 && w >= v - gv; --w)
-          if (((w % gv) & 1) == b) { last = w; break; }
-      }
-      while (pv_next <= last) {
-        const int w = pv_next++;
-        const int s = w % gv, kt = w / gv, b = s & 1;
-        AF3K_WAIT(c, BarIdx::p_ready + b, ms.pcount[b] & 1);
-        ++ms.pcount[b];
-        if (w == 0 && ms.icount > 0) AF3K_WAIT(c, BarIdx::epi_done, (ms.icount - 1) & 1);
-        tc_fence_after();
-        const uint32_t st = ms.ucount_pv % nkv;
-        const uint32_t vbase = c.smem + p.off_kv + st * kv_stage_bytes + p.k_tile_bytes;
-        const uint32_t o_tmem = c.tmem + 2 * kTile + s * p.nv;
-        const uint32_t p_tmem = c.tmem + b * kTile;
-#pragma unroll 1
-        for (int k = 0; k < kTile / 16; ++k) {
-          const uint64_t bd = make_smem_desc(vbase + k * 16 * p.v_row_bytes, p.v_tile_bytes,
-                                             8 * p.v_row_bytes, v_layout);
-          mma_ts_f16(o_tmem, p_tmem + k * 8, bd, idesc_pv, (kt > 0 || k > 0) ? 1u : 0u);
+    int qk_next = 0, pv_next = 0;
+    int qk_s = 0, pv_s = 0, pv_kt = 0;                  // stream of the next QK / PV, key tile of the next PV
+    long long idle_since = 0;
+    uint32_t idle_spins = 0;
+    while (pv_next < nu) {
+      bool progressed = false;
+      if (qk_next < nu) {
+        const int b = qk_s & 1;
+        const bool buf_free = b ? (qk_first1 || mbar_test_wait(bar_addr(c, BarIdx::s_free + 1), sfree_par1))
+                                : (qk_first0 || mbar_test_wait(bar_addr(c, BarIdx::s_free + 0), sfree_par0));
+        if (buf_free && mbar_test_wait(bar_addr(c, BarIdx::kv_full + qk_st), qk_par)) {
+          tc_fence_after();
+          const uint32_t a_lo = qd_lo + qk_s * q_step;
+          const uint32_t b_lo = kd_lo + qk_st * stage_step;
+          const uint32_t s_tmem = c.tmem + kSCol + b * kTile;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {     // one K step = 32 bytes of a tile row
+            if (k < ksteps) {
+              if (fp8) mma_ss_f8(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
+              else     mma_ss_f16(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
+            }
+          }
+          tc_commit(bar_addr(c, BarIdx::s_full + b));
+          if (b) { if (qk_first1) qk_first1 = 0; else sfree_par1 ^= 1; }
+          else   { if (qk_first0) qk_first0 = 0; else sfree_par0 ^= 1; }
+          if (++qk_st == nkv) { qk_st = 0; qk_par ^= 1; }
+          if (qk_next == nu - 1) tc_commit(bar_addr(c, BarIdx::q_empty));
+          ++qk_next;
+          if (++qk_s == gv) qk_s = 0;
+          progressed = true;
         }
-        tc_commit(bar_addr(c, BarIdx::kv_empty + st));
-        ++ms.ucount_pv;
       }
-      if (v == nu) break;
-      const int s = v % gv, b = s & 1;
-      const uint32_t st = ms.ucount_qk % nkv;
-      AF3K_WAIT(c, BarIdx::kv_full + st, (ms.ucount_qk / nkv) & 1);
-      tc_fence_after();
-      const uint32_t qbase = c.smem + p.off_q + s * p.q_tile_bytes;
-      const uint32_t kbase = c.smem + p.off_kv + st * kv_stage_bytes;
-      const uint32_t s_tmem = c.tmem + b * kTile;
-#pragma unroll 1
-      for (int k = 0; k < p.qk_ksteps; ++k) {
-        const uint64_t ad = make_smem_desc(qbase + k * 32, 16, 8 * p.qk_row_bytes, qk_layout);
-        const uint64_t bd = make_smem_desc(kbase + k * 32, 16, 8 * p.qk_row_bytes, qk_layout);
-        if (p.qk_is_fp8) mma_ss_f8(s_tmem, ad, bd, idesc_qk, k > 0 ? 1u : 0u);
-        else             mma_ss_f16(s_tmem, ad, bd, idesc_qk, k > 0 ? 1u : 0u);
+      if (pv_next < qk_next) {
+        const int b = pv_s & 1;
+        if (mbar_test_wait(bar_addr(c, BarIdx::p_ready + b), b ? pready_par1 : pready_par0)) {
+          // the previous item's epilogue must have read every O accumulator before the first
+          // P V of this item overwrites one
+          if (pv_next == 0 && icount > 0) AF3K_WAIT(c, BarIdx::epi_done, (icount - 1) & 1);
+          tc_fence_after();
+          const uint32_t b_lo = vd_lo + pv_st * stage_step;
+          const uint32_t o_tmem = c.tmem + kOCol + pv_s * p.nv;
+          const uint32_t p_tmem = c.tmem + kPCol + b * 64;
+          mma_ts_f16(o_tmem, p_tmem, b_lo, vd_hi, idesc_pv, pv_kt > 0 ? 1u : 0u);
+#pragma unroll
+          for (int k = 1; k < kTile / 16; ++k)   // 16 keys per step: 8 TMEM columns of P
+            mma_ts_f16(o_tmem, p_tmem + k * 8, b_lo + k * v_kstep, vd_hi, idesc_pv, 1u);
+          tc_commit(bar_addr(c, BarIdx::kv_empty + pv_st));
+          tc_commit(bar_addr(c, BarIdx::pv_done + b));
+          if (b) pready_par1 ^= 1; else pready_par0 ^= 1;
+          if (++pv_st == nkv) pv_st = 0;
+          ++pv_next;
+          if (++pv_s == gv) { pv_s = 0; ++pv_kt; }
+          progressed = true;
+        }
       }
-      tc_commit(bar_addr(c, BarIdx::s_full + b));
-      ++ms.ucount_qk;
-      if (v == nu - 1) tc_commit(bar_addr(c, BarIdx::q_empty));
+      if (progressed) {
+        idle_spins = 0;
+      } else {
+        if (idle_spins == 0) idle_since = clock64();
+        if ((++idle_spins & 63u) == 0u) {
+          if (*c.abort_flag != 0) return;
+          if (clock64() - idle_since > p.wait_limit) {
+            report_timeout(c, pv_next < qk_next ? BarIdx::p_ready + (pv_s & 1) : BarIdx::s_free + (qk_s & 1));
+            return;
+          }
+        }
+        __nanosleep(20);
+      }
     }
     tc_commit(bar_addr(c, BarIdx::item_done));
-    ++ms.icount;
   }
 }
 
 // ------------------------------------------------------------------ softmax
-__device__ __forceinline__ float bf16lo(uint32_t v) { return __uint_as_float(v << 16); }
-__device__ __forceinline__ float bf16hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
-
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
@@ -267,94 +307,168 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   return v;
 }
 
-// One 128 x 128 logits tile for one stream: the thread owns row `row` (TMEM lane).
-//   kMasked: some key of the tile is masked (mask words in mw).   kTail: keys >= nvalid do not exist.
-// mw[i] bit l  <->  key 4*l + i of the tile.
 // Diagnostic dump: four [128][128] float sections, row = query row of block 0's first tile:
 // raw logits, packed P words (64 used), un-normalised O (nv used), {running max, running sum}.
 constexpr int kDbgS = 0, kDbgP = kTile * kTile, kDbgO = 2 * kTile * kTile, kDbgML = 3 * kTile * kTile,
               kDbgFloats = 4 * kTile * kTile;
 
-template <bool kMasked, bool kTail>
-__device__ __forceinline__ void softmax_tile(float* dbg, uint32_t s_taddr, uint32_t o_taddr, int nv,
-                                             uint32_t bias_row, uint32_t row7, float scale,
-                                             const uint32_t (&mw)[4], int nvalid, bool first_kt,
-                                             float& m_run, float& l_run) {
-  uint32_t xr[kTile];
+// x = s * scale + bias for 64 columns [c0, c0 + 64) of the thread's row, key mask applied, row
+// maximum updated.  xr holds the raw logits on entry and x on exit.
+//   kMasked: some key of the tile is masked: mw[g] bit i <-> key 32 * g + i of the tile.
+//   kTail:   keys >= nvalid do not exist.
+template <bool kMasked, bool kTail, int kCol0>
+__device__ __forceinline__ void logits_half(uint32_t (&xr)[kTile], uint32_t bias_row, uint32_t row7,
+                                            uint64_t scale2, const uint32_t (&mw)[4], int nvalid,
+                                            float& mxa, float& mxb) {
 #pragma unroll
-  for (int cidx = 0; cidx < 4; ++cidx) tmem_ld_x32(s_taddr + cidx * 32, &xr[cidx * 32]);
-  tc_wait_ld();
-  if (dbg != nullptr) {
-#pragma unroll
-    for (int i = 0; i < kTile; ++i) dbg[kDbgS + i] = __uint_as_float(xr[i]);
-  }
-
-  float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
+  for (int j = kCol0 / 8; j < kCol0 / 8 + 8; ++j) {
     const uint4 bv = lds128(bias_row + (j >> 3) * (kBiasTileBytes / 2) + (((j & 7) ^ row7) << 4));
     const uint32_t w[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int col = j * 8 + e;
-      const float b = (e & 1) ? bf16hi(w[e >> 1]) : bf16lo(w[e >> 1]);
-      float x = fmaf(__uint_as_float(xr[col]), scale, b);
+    for (int e = 0; e < 4; ++e) {
+      const int col = j * 8 + 2 * e;
+      // bf16 pair -> two fp32: low half shifted up, high half masked in place
+      const uint64_t b2 = pack_f32x2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
+      const uint64_t s2 = pack_f32x2(__uint_as_float(xr[col]), __uint_as_float(xr[col + 1]));
+      float x0, x1;
+      unpack_f32x2(fma_f32x2(s2, scale2, b2), x0, x1);
       if (kMasked) {
-        const bool keep = (mw[col & 3] >> (col >> 2)) & 1u;
-        x = keep ? x : kMaskedLogit;
+        const uint32_t word = mw[col >> 5];
+        x0 = ((word >> (col & 31)) & 1u) ? x0 : kMaskedLogit;
+        x1 = ((word >> ((col + 1) & 31)) & 1u) ? x1 : kMaskedLogit;
       }
-      if (kTail) x = (col < nvalid) ? x : -INFINITY;
-      xr[col] = __float_as_uint(x);
-      if ((e & 3) == 0) mx0 = fmaxf(mx0, x);
-      else if ((e & 3) == 1) mx1 = fmaxf(mx1, x);
-      else if ((e & 3) == 2) mx2 = fmaxf(mx2, x);
-      else mx3 = fmaxf(mx3, x);
+      if (kTail) {
+        x0 = (col < nvalid) ? x0 : -INFINITY;
+        x1 = (col + 1 < nvalid) ? x1 : -INFINITY;
+      }
+      xr[col] = __float_as_uint(x0);
+      xr[col + 1] = __float_as_uint(x1);
+      if (e & 1) mxb = max3(mxb, x0, x1); else mxa = max3(mxa, x0, x1);
     }
   }
-  const float m_old = m_run;
-  const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m_old);
-  // exp2((m_old - m_new) * log2e): 0 on the first tile (m_old = -inf), 1 when the max stood still
-  const float alpha = ex2_approx((m_old - m_new) * kLog2e);
+}
 
-  if (!first_kt) {
-    if (__any_sync(0xffffffffu, m_new > m_old)) {
-      for (int c0 = 0; c0 < nv; c0 += 16) {
-        uint32_t o[16];
-        tmem_ld_x16(o_taddr + c0, o);
-        tc_wait_ld();
+// One 128 x 128 logits tile of one stream; the thread owns row `row` (TMEM lane).
+// m_run is the reference maximum the running sums are scaled by (it may lag the true maximum by
+// up to kLazyRescaleLog2 bits), l_run the running sum of the fp32 weights.
+template <bool kMasked, bool kTail>
+__device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, int lane,
+                                             uint32_t s_taddr, uint32_t p_taddr, uint32_t o_taddr,
+                                             int nv, uint32_t bias_row, uint32_t row7, float scale,
+                                             const uint32_t (&mw)[4], int nvalid, bool first_kt,
+                                             bool wait_prev_pv, uint32_t prev_pv_parity,
+                                             float& m_run, float& l_run) {
+  uint32_t xr[kTile];
+  tmem_ld_x32(s_taddr + 0, &xr[0]);
+  tmem_ld_x32(s_taddr + 32, &xr[32]);
+  tc_wait_ld();
+  tmem_ld_x32(s_taddr + 64, &xr[64]);
+  tmem_ld_x32(s_taddr + 96, &xr[96]);
+  if (dbg != nullptr) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-        tmem_st_x16(o_taddr + c0, o);
-      }
+    for (int i = 0; i < 64; ++i) dbg[kDbgS + i] = __uint_as_float(xr[i]);
+  }
+  const uint64_t scale2 = pack_f32x2(scale, scale);
+  float mxa = -INFINITY, mxb = -INFINITY;
+  logits_half<kMasked, kTail, 0>(xr, bias_row, row7, scale2, mw, nvalid, mxa, mxb);
+  tc_wait_ld();
+  // the logits are in registers: hand the S buffer back so that the next Q K^T can start
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::s_free + wg));
+  if (dbg != nullptr) {
+#pragma unroll
+    for (int i = 64; i < kTile; ++i) dbg[kDbgS + i] = __uint_as_float(xr[i]);
+  }
+  logits_half<kMasked, kTail, 64>(xr, bias_row, row7, scale2, mw, nvalid, mxa, mxb);
+
+  const float mt = fmaxf(mxa, mxb);
+  float m_use = m_run;
+  float alpha = 1.0f;
+  bool need = false;
+  if (first_kt) {
+    m_use = mt;
+  } else {
+    need = (mt - m_run) * kLog2e > kLazyRescaleLog2;
+    if (need) {
+      m_use = mt;
+      alpha = ex2_approx((m_run - mt) * kLog2e);
+    }
+  }
+  // P buffer and O accumulator are free once the previous P V of this warpgroup has finished
+  if (wait_prev_pv) {
+    const bool ok = mbar_wait_bounded(bar_addr(c, BarIdx::pv_done + wg), prev_pv_parity,
+                                      c.p->wait_limit, c.abort_flag);
+    if (!__all_sync(0xffffffffu, ok)) {
+      report_timeout(c, BarIdx::pv_done + wg);
+      return false;
+    }
+    tc_fence_after();
+  }
+  if (__any_sync(0xffffffffu, need)) {
+    for (int c0 = 0; c0 < nv; c0 += 16) {
+      uint32_t o[16];
+      tmem_ld_x16(o_taddr + c0, o);
+      tc_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+      tmem_st_x16(o_taddr + c0, o);
     }
   }
 
-  const float neg_mc = -m_new * kLog2e;
-  float sm0 = 0.f, sm1 = 0.f, sm2 = 0.f, sm3 = 0.f;
+  const float neg_mc = -m_use * kLog2e;
+  const uint64_t l2e2 = pack_f32x2(kLog2e, kLog2e);
+  const uint64_t nmc2 = pack_f32x2(neg_mc, neg_mc);
+  uint64_t suma = pack_f32x2(0.f, 0.f), sumb = suma;
 #pragma unroll
   for (int cidx = 0; cidx < 8; ++cidx) {
     uint32_t pk[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int col = cidx * 16 + 2 * i;
-      const float p0 = ex2_approx(fmaf(__uint_as_float(xr[col]), kLog2e, neg_mc));
-      const float p1 = ex2_approx(fmaf(__uint_as_float(xr[col + 1]), kLog2e, neg_mc));
-      if (i & 1) { sm2 += p0; sm3 += p1; } else { sm0 += p0; sm1 += p1; }
+      float y0, y1;
+      unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(xr[col]), __uint_as_float(xr[col + 1])), l2e2, nmc2),
+                   y0, y1);
+      const float p0 = ex2_approx(y0);
+      const float p1 = ex2_approx(y1);
+      if (i & 1) sumb = add_f32x2(sumb, pack_f32x2(p0, p1));
+      else       suma = add_f32x2(suma, pack_f32x2(p0, p1));
       pk[i] = pack_bf16x2(p0, p1);
     }
     if (dbg != nullptr) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) dbg[kDbgP + cidx * 8 + i] = __uint_as_float(pk[i]);
     }
-    // P (bf16, two keys per 32-bit column) overwrites the first 64 columns of the S buffer
+    // P as bf16, two keys per 32-bit TMEM column: the A operand of the second GEMM
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
                  ::"r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
-                 "r"(pk[6]), "r"(pk[7]), "r"(s_taddr + cidx * 8)
+                 "r"(pk[6]), "r"(pk[7]), "r"(p_taddr + cidx * 8)
                  : "memory");
   }
   tc_wait_st();
-  m_run = m_new;
-  l_run = l_run * alpha + ((sm0 + sm1) + (sm2 + sm3));
+  float s0, s1, s2, s3;
+  unpack_f32x2(suma, s0, s1);
+  unpack_f32x2(sumb, s2, s3);
+  m_run = m_use;
+  l_run = l_run * alpha + ((s0 + s1) + (s2 + s3));
+  return true;
+}
+
+// Key-mask flags of one (pair row, key tile) for this lane: bit g = key 32 * g + lane is attended.
+__device__ __forceinline__ uint32_t load_mask_flags(const AttnParams& p, int pair_row, int kt, int lane) {
+  uint32_t f = 0xFu;
+  if (p.mask != nullptr) {
+    const uint8_t* mrow = p.mask + (long long)pair_row * p.mask_row_stride;
+    const int k0 = kt * kTile + lane;
+    f = 0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int key = k0 + 32 * g;
+      const bool keep = (key < p.Sk) ? (mrow[key] != 0) : true;
+      f |= (keep ? 1u : 0u) << g;
+    }
+  }
+  return f;
 }
 
 template <bool kDebug>
@@ -362,16 +476,19 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
   const AttnParams& p = *c.p;
   const int row = wq * 32 + lane;                    // row of the 128-query tile == TMEM lane
   const uint32_t lane_sel = (uint32_t)(wq * 32) << 16;
-  const uint32_t s_taddr = c.tmem + lane_sel + wg * kTile;
+  const uint32_t s_taddr = c.tmem + lane_sel + kSCol + wg * kTile;
+  const uint32_t p_taddr = c.tmem + lane_sel + kPCol + wg * 64;
   float* st_m = reinterpret_cast<float*>(__cvta_shared_to_generic(c.smem + p.off_state));
   float* st_l = st_m + kMaxStreams * kTile;
-  uint32_t scnt = 0, bcount = 0, icount = 0;
+  uint32_t ucnt = 0, bcount = 0, icount = 0;         // tiles done by this warpgroup, bias tiles, items
   const int tail_keys = p.Sk - (p.n_kt - 1) * kTile;   // keys present in the last key tile
 
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
     const Item it = decode_item(p, item);
     float scale = p.scale;
     if (p.q_scale != nullptr) scale *= p.q_scale[it.h] * p.k_scale[it.h];
+    // mask flags are fetched one tile ahead so that the load is off the critical path
+    uint32_t flags_next = (wg < it.gv) ? load_mask_flags(p, it.r0 + wg, 0, lane) : 0xFu;
 
     for (int kt = 0; kt < p.n_kt; ++kt) {
       const uint32_t bst = bcount % kBiasStages;
@@ -380,38 +497,38 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
       const bool is_tail = (kt == p.n_kt - 1) && (tail_keys != kTile);
 
       for (int s = wg; s < it.gv; s += 2) {
-        // key-mask bits of this (pair row, key tile): lane l fetches keys 4l .. 4l+3
-        uint32_t mw[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-        if (p.mask != nullptr) {
-          const uint8_t* mrow = p.mask + (long long)(it.r0 + s) * p.mask_row_stride;
-          const int k0 = kt * kTile + 4 * lane;
+        const uint32_t flags = flags_next;
+        if (s + 2 < it.gv) flags_next = load_mask_flags(p, it.r0 + s + 2, kt, lane);
+        else if (kt + 1 < p.n_kt) flags_next = load_mask_flags(p, it.r0 + wg, kt + 1, lane);
+        uint32_t mw[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const bool keep = (k0 + i < p.Sk) ? (mrow[k0 + i] != 0) : true;
-            mw[i] = __ballot_sync(0xffffffffu, keep);
-          }
-        }
+        for (int g = 0; g < 4; ++g) mw[g] = __ballot_sync(0xffffffffu, (flags >> g) & 1u);
         const bool all_keep = (mw[0] & mw[1] & mw[2] & mw[3]) == 0xffffffffu;
 
         float m_run = -INFINITY, l_run = 0.f;
         if (kt > 0) { m_run = st_m[s * kTile + row]; l_run = st_l[s * kTile + row]; }
 
-        AF3K_WAIT_WARP(c, BarIdx::s_full + wg, scnt & 1);
-        ++scnt;
+        AF3K_WAIT_WARP(c, BarIdx::s_full + wg, ucnt & 1);
         tc_fence_after();
-        const uint32_t o_taddr = c.tmem + lane_sel + 2 * kTile + s * p.nv;
+        const uint32_t o_taddr = c.tmem + lane_sel + kOCol + s * p.nv;
         float* dbg = nullptr;
         if (kDebug && p.debug != nullptr && blockIdx.x == 0 && icount == 0 && s == 0 && kt == 0)
           dbg = p.debug + (size_t)row * kTile;
+        bool ok;
         if (is_tail)
-          softmax_tile<true, true>(dbg, s_taddr, o_taddr, p.nv, bias_row, row & 7, scale, mw, tail_keys,
-                                   kt == 0, m_run, l_run);
+          ok = softmax_tile<true, true>(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row,
+                                        row & 7, scale, mw, tail_keys, kt == 0, ucnt > 0,
+                                        (ucnt - 1) & 1, m_run, l_run);
         else if (!all_keep)
-          softmax_tile<true, false>(dbg, s_taddr, o_taddr, p.nv, bias_row, row & 7, scale, mw, kTile,
-                                    kt == 0, m_run, l_run);
+          ok = softmax_tile<true, false>(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row,
+                                         row & 7, scale, mw, kTile, kt == 0, ucnt > 0,
+                                         (ucnt - 1) & 1, m_run, l_run);
         else
-          softmax_tile<false, false>(dbg, s_taddr, o_taddr, p.nv, bias_row, row & 7, scale, mw, kTile,
-                                     kt == 0, m_run, l_run);
+          ok = softmax_tile<false, false>(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row,
+                                          row & 7, scale, mw, kTile, kt == 0, ucnt > 0,
+                                          (ucnt - 1) & 1, m_run, l_run);
+        if (!ok) return;
+        ++ucnt;
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::p_ready + wg));
@@ -429,7 +546,7 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
     const int qrow = it.qt * kTile + row;
     for (int s = wg; s < it.gv; s += 2) {
       const float inv = 1.0f / st_l[s * kTile + row];
-      const uint32_t o_taddr = c.tmem + lane_sel + 2 * kTile + s * p.nv;
+      const uint32_t o_taddr = c.tmem + lane_sel + kOCol + s * p.nv;
       __nv_bfloat16* orow = p.out + (long long)(it.r0 + s) * p.out_stride_b1 +
                             (long long)it.h * p.out_stride_b2 + (long long)qrow * p.out_stride_s;
       for (int c0 = 0; c0 < p.nv; c0 += 16) {
@@ -495,7 +612,9 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
     mbar_init(bar_addr(c, BarIdx::epi_done), 8);
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_addr(c, BarIdx::s_full + i), 1);
+      mbar_init(bar_addr(c, BarIdx::s_free + i), 4);
       mbar_init(bar_addr(c, BarIdx::p_ready + i), 4);
+      mbar_init(bar_addr(c, BarIdx::pv_done + i), 1);
     }
     for (int i = 0; i < kBiasStages; ++i) {
       mbar_init(bar_addr(c, BarIdx::bias_full + i), 1);
@@ -516,11 +635,16 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
   tc_fence_after();
   c.tmem = tmem_base_slot;
 
-  if (warp == 0) {
-    if (lane == 0) producer_role(c, &tm_q, &tm_k, &tm_v, &tm_bias);
-  } else if (warp == 1) {
-    if (lane == 0) mma_role(c);
-  } else if (warp >= 4) {
+  if (warp < 4) {
+    // warps 0-3 need few registers; the two softmax warpgroups take what they give up
+    setmaxnreg_dec<kRegsMisc>();
+    if (warp == 0) {
+      if (lane == 0) producer_role(c, &tm_q, &tm_k, &tm_v, &tm_bias);
+    } else if (warp == 1) {
+      if (lane == 0) mma_role(c);
+    }
+  } else {
+    setmaxnreg_inc<kRegsSoftmax>();
     softmax_role<kDebug>(c, (warp - 4) >> 2, warp & 3, lane);
   }
 

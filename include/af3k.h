@@ -61,7 +61,7 @@ typedef struct af3k_attention_desc {
   int32_t qk_dtype;       /* AF3K_BF16 or AF3K_FP8_E4M3 */
   int32_t bias_dtype;     /* AF3K_BF16 or AF3K_F32 */
   float softmax_scale;    /* the reference uses 1/sqrt(D) */
-  int32_t rows_per_item;  /* 0 = choose; else pair rows that share one staged bias tile (1..8) */
+  int32_t rows_per_item;  /* 0 = choose; else requested pair rows per staged bias tile (1..8, clamped to what fits) */
 } af3k_attention_desc;
 
 /* Library / ABI version (major * 1000 + minor). */
