@@ -166,7 +166,9 @@ int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
   p.scale = d.softmax_scale;
 
   const int budget = dev.max_smem_optin - 1024 /*alignment slack*/ - kStaticSmemReserve;
-  const int fixed = kBiasStages * kBiasTileBytes + kMaxStreams * kTile * 8 + 256 /*barriers*/;
+  p.mask_col = 1;   // set for real in the launch path once the mask pointer is known
+  const int fixed = kBiasStages * kBiasTileBytes + kMaxStreams * kTile * 8 + 256 /*barriers*/ +
+                    (kMaxKvStages + 2) * (int)kMaskPanelBytes /*ones column, mask ring, zero block*/;
   const int kv_stage = (int)(p.k_tile_bytes + p.v_tile_bytes);
   const int g_tmem = (int)((kTmemCols - kOCol) / p.nv);
   int g_max = kMaxStreams < g_tmem ? kMaxStreams : g_tmem;
@@ -204,6 +206,9 @@ int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
   p.off_bias = off;   off += kBiasStages * kBiasTileBytes;
   p.off_state = off;  off += kMaxStreams * kTile * 8;
   p.off_bar = off;    off += 256;
+  p.off_ones = off;   off += kMaskPanelBytes;
+  p.off_mcol = off;   off += kMaxKvStages * kMaskPanelBytes;
+  p.off_zero = off;   off += kMaskPanelBytes;
   size_t smem = off + 1024;
   // One CTA per SM is required (each CTA allocates all of TMEM): ask for more than half the SM's
   // shared memory even when the tiles need less.
@@ -393,6 +398,7 @@ int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, c
   p.k_scale = k_scale;
   p.mask = mask;
   p.mask_row_stride = d.mask_row_stride;
+  p.mask_col = (mask != nullptr || d.Sk % kTile != 0) ? 1 : 0;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.out_stride_b1 = d.out_stride[0];
   p.out_stride_b2 = d.out_stride[1];

@@ -7,6 +7,7 @@
 //   warp 0      TMA producer: Q tiles, K/V ring, bias ring (cp.async.bulk.tensor, no multicast)
 //   warp 1      tcgen05.mma issuer: S = Q K^T (smem x smem -> TMEM), O += P V (TMEM x smem -> TMEM)
 //   warp 2      TMEM allocator
+//   warp 3      key-mask writer: one bf16 "mask column" per logits tile (see below)
 //   warps 4-7   softmax warpgroup 0 (owns S / P buffer 0 and the even streams of a work item)
 //   warps 8-11  softmax warpgroup 1 (owns S / P buffer 1 and the odd streams)
 //
@@ -14,6 +15,13 @@
 // the same bias tiles, so one staged bias tile serves G logits tiles; each stream has its own
 // Q tile, K/V tiles, fp32 running max / sum and O accumulator in TMEM.  One softmax thread owns
 // one query row (TMEM lane), so row max / row sum need no cross-thread traffic.
+//
+// The key mask costs the softmax threads nothing: the first GEMM gets one extra K step whose A
+// operand is a constant column of ones and whose B operand holds, per key, 0 (attend), -2^47
+// (masked) or -inf (beyond the sequence).  The tensor core adds that value to every logit of the
+// key's column, so a masked key ends up with weight exactly 0, a row whose keys are all masked
+// with uniform weights over its real keys (what "fill with -1e9, then softmax" gives), and a key
+// that does not exist with weight 0 always.
 //
 // Logits stay fp32 from the tensor core to the exponential; P is rounded to bf16 once, when it
 // is written to TMEM as the A operand of the second GEMM.  S and P live in separate TMEM columns:
@@ -42,10 +50,11 @@ constexpr int kBiasStages = 2;
 constexpr int kBiasTileBytes = kTile * kTile * 2;  // bf16, two 128B-swizzled boxes of 64 columns
 constexpr int kMaxKvStages = 6;
 constexpr uint32_t kTmemCols = 512;
-// Stand-in for the reference's "-1e9" fill of masked keys.  -2^30 keeps the same meaning (weight
-// exactly 0 unless every key of the row is masked, then uniform) and its product with log2(e) is
-// exact in fp32, so a fully masked row sees exponent 0 rather than a rounding residue.
-constexpr float kMaskedLogit = -1073741824.0f;
+// bf16 bit patterns of the mask column.  -2^47 stands in for the reference's "-1e9" fill: added
+// in fp32 to any logit below 2^23 in magnitude it gives exactly -2^47, so all masked keys of a
+// row are equal (uniform weights when nothing else is left) and vanish next to any real key.
+constexpr uint16_t kMaskColKeep = 0x0000, kMaskColMasked = 0xD700, kMaskColAbsent = 0xFF80;
+constexpr uint32_t kMaskPanelBytes = 2048;   // 128 keys x one 16-byte core-matrix row
 constexpr float kLog2e = 1.4426950408889634f;
 
 enum StatusBits : int {
@@ -76,6 +85,11 @@ struct AttnParams {
   float* debug;          // diagnostic dump of block 0's first logits tile (debug build of the kernel)
   uint32_t q_tile_bytes, k_tile_bytes, v_tile_bytes;
   uint32_t off_q, off_kv, off_bias, off_state, off_bar;   // from the 1024-aligned smem base
+  // mask-column operands of the extra K step (all no-swizzle, K-major, 16-byte rows):
+  //   off_ones: A operand, element (row, 0) = 1;  off_mcol: ring of per-tile B operands, element
+  //   (key, 0) = mask value;  off_zero: the all-zero second half of K shared by both.
+  uint32_t off_ones, off_mcol, off_zero;
+  int mask_col;          // 1: the extra K step runs (a mask was given or Sk is not a tile multiple)
 };
 
 // Barrier slots inside the barrier block (8 bytes each).
@@ -189,6 +203,41 @@ __device__ void producer_role(const Ctx& c, const CUtensorMap* tm_q, const CUten
   }
 }
 
+// ------------------------------------------------------------------ key-mask writer (one warp)
+// For every logits tile, in the producer's order: 128 mask values (bf16) into the tile's slot of
+// the mask-column ring.  The slot is the B operand of the extra K step; only element 0 of each
+// key's 16-byte row changes, the rest stays zero.  Arrives on the tile's kv_full barrier (which
+// then counts two arrivals: this one and the producer's).
+__device__ void mask_writer_role(const Ctx& c, int lane) {
+  const AttnParams& p = *c.p;
+  const uint32_t nkv = p.kv_stages;
+  uint32_t st = 0, round = 0;      // ring slot and how many times the ring wrapped
+  for (int item = blockIdx.x; item < p.n_items; item += gridDim.x) {
+    const Item it = decode_item(p, item);
+    for (int kt = 0; kt < p.n_kt; ++kt) {
+      for (int s = 0; s < it.gv; ++s) {
+        uint16_t val[4];
+        const uint8_t* mrow = p.mask != nullptr ? p.mask + (long long)(it.r0 + s) * p.mask_row_stride : nullptr;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int key = kt * kTile + 32 * g + lane;
+          val[g] = key >= p.Sk ? kMaskColAbsent
+                               : ((mrow == nullptr || mrow[key] != 0) ? kMaskColKeep : kMaskColMasked);
+        }
+        if (round > 0) AF3K_WAIT_WARP(c, BarIdx::kv_empty + st, (round - 1) & 1);
+        const uint32_t slot = c.smem + p.off_mcol + st * kMaskPanelBytes;
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          asm volatile("st.shared.u16 [%0], %1;" ::"r"(slot + (32 * g + lane) * 16), "h"(val[g]) : "memory");
+        fence_proxy_async_smem();    // make the generic-proxy stores visible to the tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::kv_full + st));
+        if (++st == nkv) { st = 0; ++round; }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ MMA issuer (one thread)
 // Event loop: a Q K^T is issued as soon as its S buffer was released and its K/V stage landed, a
 // P V as soon as its P was written.  Both conditions are polled without blocking, so neither can
@@ -213,6 +262,14 @@ __device__ void mma_role(const Ctx& c) {
   const uint32_t v_kstep = (16u * p.v_row_bytes) >> 4;
   const int ksteps = p.qk_ksteps;
   const bool fp8 = p.qk_is_fp8 != 0;
+  // extra K step: ones column x mask column, both K-major without swizzle (8-row groups 128 bytes
+  // apart, the second 16-byte half of K in the shared zero block)
+  const uint64_t od0 = make_smem_desc(c.smem + p.off_ones, p.off_zero - p.off_ones, 128, 0);
+  const uint64_t md0 = make_smem_desc(c.smem + p.off_mcol, p.off_zero - p.off_mcol, 128, 0);
+  const uint32_t od_lo = (uint32_t)od0, od_hi = (uint32_t)(od0 >> 32);
+  const uint32_t md_lo = (uint32_t)md0, md_hi = (uint32_t)(md0 >> 32);
+  const uint32_t idesc_mask = make_idesc(1u, 1u, 0u, 0u, kTile);
+  const bool mask_col = p.mask_col != 0;
   // ring positions / barrier parities are carried incrementally: no division on this thread
   uint32_t qk_st = 0, qk_par = 0, pv_st = 0;           // K/V stage of the next QK / PV, kv_full parity
   uint32_t icount = 0;
@@ -246,6 +303,11 @@ __device__ void mma_role(const Ctx& c) {
               if (fp8) mma_ss_f8(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
               else     mma_ss_f16(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
             }
+          }
+          if (mask_col) {
+            // start address and leading offset both move with the ring slot: the zero block stays put
+            const uint32_t slot16 = qk_st * (kMaskPanelBytes >> 4);
+            mma_ss_f16(s_tmem, od_lo, od_hi, md_lo + slot16 - (slot16 << 16), md_hi, idesc_mask, 1u);
           }
           tc_commit(bar_addr(c, BarIdx::s_full + b));
           if (b) { if (qk_first1) qk_first1 = 0; else sfree_par1 ^= 1; }
@@ -312,14 +374,12 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 constexpr int kDbgS = 0, kDbgP = kTile * kTile, kDbgO = 2 * kTile * kTile, kDbgML = 3 * kTile * kTile,
               kDbgFloats = 4 * kTile * kTile;
 
-// x = s * scale + bias for 64 columns [c0, c0 + 64) of the thread's row, key mask applied, row
-// maximum updated.  xr holds the raw logits on entry and x on exit.
-//   kMasked: some key of the tile is masked: mw[g] bit i <-> key 32 * g + i of the tile.
-//   kTail:   keys >= nvalid do not exist.
-template <bool kMasked, bool kTail, int kCol0>
+// x = s * scale + bias for the 64 columns [kCol0, kCol0 + 64) of the thread's row, row maximum
+// updated.  xr holds the raw logits on entry and x on exit.  Masked and absent keys arrive from
+// the tensor core as -2^47 and -inf and need no handling here.
+template <int kCol0>
 __device__ __forceinline__ void logits_half(uint32_t (&xr)[kTile], uint32_t bias_row, uint32_t row7,
-                                            uint64_t scale2, const uint32_t (&mw)[4], int nvalid,
-                                            float& mxa, float& mxb) {
+                                            uint64_t scale2, float& mxa, float& mxb) {
 #pragma unroll
   for (int j = kCol0 / 8; j < kCol0 / 8 + 8; ++j) {
     const uint4 bv = lds128(bias_row + (j >> 3) * (kBiasTileBytes / 2) + (((j & 7) ^ row7) << 4));
@@ -332,15 +392,6 @@ __device__ __forceinline__ void logits_half(uint32_t (&xr)[kTile], uint32_t bias
       const uint64_t s2 = pack_f32x2(__uint_as_float(xr[col]), __uint_as_float(xr[col + 1]));
       float x0, x1;
       unpack_f32x2(fma_f32x2(s2, scale2, b2), x0, x1);
-      if (kMasked) {
-        const uint32_t word = mw[col >> 5];
-        x0 = ((word >> (col & 31)) & 1u) ? x0 : kMaskedLogit;
-        x1 = ((word >> ((col + 1) & 31)) & 1u) ? x1 : kMaskedLogit;
-      }
-      if (kTail) {
-        x0 = (col < nvalid) ? x0 : -INFINITY;
-        x1 = (col + 1 < nvalid) ? x1 : -INFINITY;
-      }
       xr[col] = __float_as_uint(x0);
       xr[col + 1] = __float_as_uint(x1);
       if (e & 1) mxb = max3(mxb, x0, x1); else mxa = max3(mxa, x0, x1);
@@ -351,12 +402,10 @@ __device__ __forceinline__ void logits_half(uint32_t (&xr)[kTile], uint32_t bias
 // One 128 x 128 logits tile of one stream; the thread owns row `row` (TMEM lane).
 // m_run is the reference maximum the running sums are scaled by (it may lag the true maximum by
 // up to kLazyRescaleLog2 bits), l_run the running sum of the fp32 weights.
-template <bool kMasked, bool kTail>
 __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, int lane,
                                              uint32_t s_taddr, uint32_t p_taddr, uint32_t o_taddr,
                                              int nv, uint32_t bias_row, uint32_t row7, float scale,
-                                             const uint32_t (&mw)[4], int nvalid, bool first_kt,
-                                             bool wait_prev_pv, uint32_t prev_pv_parity,
+                                             bool first_kt, bool wait_prev_pv, uint32_t prev_pv_parity,
                                              float& m_run, float& l_run) {
   uint32_t xr[kTile];
   tmem_ld_x32(s_taddr + 0, &xr[0]);
@@ -370,7 +419,7 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
   }
   const uint64_t scale2 = pack_f32x2(scale, scale);
   float mxa = -INFINITY, mxb = -INFINITY;
-  logits_half<kMasked, kTail, 0>(xr, bias_row, row7, scale2, mw, nvalid, mxa, mxb);
+  logits_half<0>(xr, bias_row, row7, scale2, mxa, mxb);
   tc_wait_ld();
   // the logits are in registers: hand the S buffer back so that the next Q K^T can start
   tc_fence_before();
@@ -380,7 +429,7 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
 #pragma unroll
     for (int i = 64; i < kTile; ++i) dbg[kDbgS + i] = __uint_as_float(xr[i]);
   }
-  logits_half<kMasked, kTail, 64>(xr, bias_row, row7, scale2, mw, nvalid, mxa, mxb);
+  logits_half<64>(xr, bias_row, row7, scale2, mxa, mxb);
 
   const float mt = fmaxf(mxa, mxb);
   float m_use = m_run;
@@ -416,9 +465,10 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
     }
   }
 
-  const float neg_mc = -m_use * kLog2e;
+  // p = exp2((x - m) * log2e).  The subtraction comes first so that x == m gives exactly 0 even
+  // for the huge negative values of masked keys (a row with no attended key: all weights 1).
   const uint64_t l2e2 = pack_f32x2(kLog2e, kLog2e);
-  const uint64_t nmc2 = pack_f32x2(neg_mc, neg_mc);
+  const uint64_t nm2 = pack_f32x2(-m_use, -m_use);
   uint64_t suma = pack_f32x2(0.f, 0.f), sumb = suma;
 #pragma unroll
   for (int cidx = 0; cidx < 8; ++cidx) {
@@ -427,8 +477,8 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
     for (int i = 0; i < 8; ++i) {
       const int col = cidx * 16 + 2 * i;
       float y0, y1;
-      unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(xr[col]), __uint_as_float(xr[col + 1])), l2e2, nmc2),
-                   y0, y1);
+      const uint64_t d2 = add_f32x2(pack_f32x2(__uint_as_float(xr[col]), __uint_as_float(xr[col + 1])), nm2);
+      unpack_f32x2(mul_f32x2(d2, l2e2), y0, y1);
       const float p0 = ex2_approx(y0);
       const float p1 = ex2_approx(y1);
       if (i & 1) sumb = add_f32x2(sumb, pack_f32x2(p0, p1));
@@ -454,23 +504,6 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
   return true;
 }
 
-// Key-mask flags of one (pair row, key tile) for this lane: bit g = key 32 * g + lane is attended.
-__device__ __forceinline__ uint32_t load_mask_flags(const AttnParams& p, int pair_row, int kt, int lane) {
-  uint32_t f = 0xFu;
-  if (p.mask != nullptr) {
-    const uint8_t* mrow = p.mask + (long long)pair_row * p.mask_row_stride;
-    const int k0 = kt * kTile + lane;
-    f = 0;
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      const int key = k0 + 32 * g;
-      const bool keep = (key < p.Sk) ? (mrow[key] != 0) : true;
-      f |= (keep ? 1u : 0u) << g;
-    }
-  }
-  return f;
-}
-
 template <bool kDebug>
 __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
   const AttnParams& p = *c.p;
@@ -481,30 +514,18 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
   float* st_m = reinterpret_cast<float*>(__cvta_shared_to_generic(c.smem + p.off_state));
   float* st_l = st_m + kMaxStreams * kTile;
   uint32_t ucnt = 0, bcount = 0, icount = 0;         // tiles done by this warpgroup, bias tiles, items
-  const int tail_keys = p.Sk - (p.n_kt - 1) * kTile;   // keys present in the last key tile
 
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
     const Item it = decode_item(p, item);
     float scale = p.scale;
     if (p.q_scale != nullptr) scale *= p.q_scale[it.h] * p.k_scale[it.h];
-    // mask flags are fetched one tile ahead so that the load is off the critical path
-    uint32_t flags_next = (wg < it.gv) ? load_mask_flags(p, it.r0 + wg, 0, lane) : 0xFu;
 
     for (int kt = 0; kt < p.n_kt; ++kt) {
       const uint32_t bst = bcount % kBiasStages;
       AF3K_WAIT_WARP(c, BarIdx::bias_full + bst, (bcount / kBiasStages) & 1);
       const uint32_t bias_row = c.smem + p.off_bias + bst * kBiasTileBytes + row * 128;
-      const bool is_tail = (kt == p.n_kt - 1) && (tail_keys != kTile);
 
       for (int s = wg; s < it.gv; s += 2) {
-        const uint32_t flags = flags_next;
-        if (s + 2 < it.gv) flags_next = load_mask_flags(p, it.r0 + s + 2, kt, lane);
-        else if (kt + 1 < p.n_kt) flags_next = load_mask_flags(p, it.r0 + wg, kt + 1, lane);
-        uint32_t mw[4];
-#pragma unroll
-        for (int g = 0; g < 4; ++g) mw[g] = __ballot_sync(0xffffffffu, (flags >> g) & 1u);
-        const bool all_keep = (mw[0] & mw[1] & mw[2] & mw[3]) == 0xffffffffu;
-
         float m_run = -INFINITY, l_run = 0.f;
         if (kt > 0) { m_run = st_m[s * kTile + row]; l_run = st_l[s * kTile + row]; }
 
@@ -514,20 +535,9 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
         float* dbg = nullptr;
         if (kDebug && p.debug != nullptr && blockIdx.x == 0 && icount == 0 && s == 0 && kt == 0)
           dbg = p.debug + (size_t)row * kTile;
-        bool ok;
-        if (is_tail)
-          ok = softmax_tile<true, true>(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row,
-                                        row & 7, scale, mw, tail_keys, kt == 0, ucnt > 0,
-                                        (ucnt - 1) & 1, m_run, l_run);
-        else if (!all_keep)
-          ok = softmax_tile<true, false>(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row,
-                                         row & 7, scale, mw, kTile, kt == 0, ucnt > 0,
-                                         (ucnt - 1) & 1, m_run, l_run);
-        else
-          ok = softmax_tile<false, false>(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row,
-                                          row & 7, scale, mw, kTile, kt == 0, ucnt > 0,
-                                          (ucnt - 1) & 1, m_run, l_run);
-        if (!ok) return;
+        if (!softmax_tile(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row, row & 7, scale,
+                          kt == 0, ucnt > 0, (ucnt - 1) & 1, m_run, l_run))
+          return;
         ++ucnt;
         tc_fence_before();
         __syncwarp();
@@ -621,7 +631,7 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
       mbar_init(bar_addr(c, BarIdx::bias_empty + i), 8);
     }
     for (int i = 0; i < kMaxKvStages; ++i) {
-      mbar_init(bar_addr(c, BarIdx::kv_full + i), 1);
+      mbar_init(bar_addr(c, BarIdx::kv_full + i), p.mask_col ? 2 : 1);
       mbar_init(bar_addr(c, BarIdx::kv_empty + i), 1);
     }
     fence_barrier_init();
@@ -629,6 +639,18 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
   if (warp == 2) {
     tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
     tmem_relinquish();
+  }
+  if (warp == 3 && p.mask_col) {
+    // ones column, mask-column ring and zero block are contiguous: clear them, then set
+    // element (row, 0) of the ones operand to bf16 1.0
+    const uint32_t base = c.smem + p.off_ones;
+    const uint32_t bytes = p.off_zero + kMaskPanelBytes - p.off_ones;
+    for (uint32_t o = lane * 16; o < bytes; o += 32 * 16)
+      asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(base + o), "r"(0u) : "memory");
+    __syncwarp();
+    for (int r = lane; r < kTile; r += 32)
+      asm volatile("st.shared.u16 [%0], %1;" ::"r"(base + r * 16), "h"((uint16_t)0x3F80) : "memory");
+    fence_proxy_async_smem();
   }
   tc_fence_before();
   __syncthreads();
@@ -642,6 +664,8 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
       if (lane == 0) producer_role(c, &tm_q, &tm_k, &tm_v, &tm_bias);
     } else if (warp == 1) {
       if (lane == 0) mma_role(c);
+    } else if (warp == 3) {
+      if (p.mask_col) mask_writer_role(c, lane);
     }
   } else {
     setmaxnreg_inc<kRegsSoftmax>();
