@@ -5,8 +5,8 @@
 // softmax -> BRGEMM) with one persistent warp-specialised kernel:
 //
 //   warp 0      TMA producer: Q tiles, K/V ring, bias ring (cp.async.bulk.tensor, no multicast)
-//   warp 1      tcgen05.mma issuer: S = Q K^T (smem x smem -> TMEM), O += P V (TMEM x smem -> TMEM)
-//   warp 2      TMEM allocator
+//   warp 1      tcgen05.mma issuer for S = Q K^T (smem x smem -> TMEM)
+//   warp 2      TMEM allocator, then tcgen05.mma issuer for O += P V (TMEM x smem -> TMEM)
 //   warp 3      key-mask writer: one bf16 "mask column" per logits tile (see below)
 //   warps 4-7   softmax warpgroup 0 (owns S / P buffer 0 and the even streams of a work item)
 //   warps 8-11  softmax warpgroup 1 (owns S / P buffer 1 and the odd streams)
@@ -98,13 +98,19 @@ struct BarIdx {
   static constexpr int s_full = 4;      // [2]  Q K^T of a tile finished
   static constexpr int s_free = 6;      // [2]  softmax warpgroup has the logits in registers
   static constexpr int p_ready = 8;     // [2]  P written (and O rescaled if needed)
-  static constexpr int pv_done = 10;    // [2]  P V of a tile finished: P buffer and O are free
+  // (slots 10, 11 unused)  P V completion is signalled on the tile's kv_empty barrier
   static constexpr int bias_full = 12;  // [kBiasStages]
   static constexpr int bias_empty = 14; // [kBiasStages]
   static constexpr int kv_full = 16;    // [kMaxKvStages]
   static constexpr int kv_empty = 16 + kMaxKvStages;
   static constexpr int count = 16 + 2 * kMaxKvStages;
 };
+
+// Diagnostic dump: four [128][128] float sections, row = query row of block 0's first tile:
+// raw logits, packed P words (64 used), un-normalised O (nv used), {running max, running sum}.
+constexpr int kDbgTimelineTiles = 256;   // per warpgroup; 8 clock values each, after kDbgFloats floats
+constexpr int kDbgS = 0, kDbgP = kTile * kTile, kDbgO = 2 * kTile * kTile, kDbgML = 3 * kTile * kTile,
+              kDbgFloats = 4 * kTile * kTile;
 
 struct Ctx {
   const AttnParams* p;
@@ -238,30 +244,28 @@ __device__ void mask_writer_role(const Ctx& c, int lane) {
   }
 }
 
-// ------------------------------------------------------------------ MMA issuer (one thread)
-// Event loop: a Q K^T is issued as soon as its S buffer was released and its K/V stage landed, a
-// P V as soon as its P was written.  Both conditions are polled without blocking, so neither can
-// starve the other whatever the number of streams per item.
-__device__ void mma_role(const Ctx& c) {
+// ------------------------------------------------------------------ MMA issuers (two threads)
+// Issuing a tcgen05.mma costs its thread tens to hundreds of cycles, and the tiles here are small
+// (N = 128, K = 16 and N = D, K = 16), so one thread issuing both GEMMs of every tile was the
+// limiter of the whole kernel.  The two GEMMs are therefore issued by two threads in two warps:
+// they touch different TMEM columns and every hand-over between them goes through an mbarrier,
+// so no ordering between the two instruction streams is assumed.
+
+// S = Q K^T (+ mask column) for every tile, in order.
+__device__ void qk_issuer_role(const Ctx& c) {
   const AttnParams& p = *c.p;
   const uint32_t nkv = p.kv_stages;
   const uint32_t qk_layout = swizzle_layout_code(p.qk_row_bytes);
-  const uint32_t v_layout = swizzle_layout_code(p.v_row_bytes);
-  const uint32_t idesc_qk = make_idesc(p.qk_is_fp8 ? 0u : 1u, p.qk_is_fp8 ? 0u : 1u, 0u, 0u, kTile);
-  const uint32_t idesc_pv = make_idesc(1u, 1u, 0u, 1u, (uint32_t)p.nv);
+  const bool fp8 = p.qk_is_fp8 != 0;
+  const uint32_t idesc_qk = make_idesc(fp8 ? 0u : 1u, fp8 ? 0u : 1u, 0u, 0u, kTile);
   const uint32_t kv_stage_bytes = p.k_tile_bytes + p.v_tile_bytes;
   // descriptor words for tile 0 / stage 0; later tiles only move the start-address field
   const uint64_t qd0 = make_smem_desc(c.smem + p.off_q, 16, 8 * p.qk_row_bytes, qk_layout);
   const uint64_t kd0 = make_smem_desc(c.smem + p.off_kv, 16, 8 * p.qk_row_bytes, qk_layout);
-  const uint64_t vd0 = make_smem_desc(c.smem + p.off_kv + p.k_tile_bytes, p.v_tile_bytes,
-                                      8 * p.v_row_bytes, v_layout);
   const uint32_t qd_lo = (uint32_t)qd0, qd_hi = (uint32_t)(qd0 >> 32);
   const uint32_t kd_lo = (uint32_t)kd0, kd_hi = (uint32_t)(kd0 >> 32);
-  const uint32_t vd_lo = (uint32_t)vd0, vd_hi = (uint32_t)(vd0 >> 32);
   const uint32_t q_step = p.q_tile_bytes >> 4, stage_step = kv_stage_bytes >> 4;
-  const uint32_t v_kstep = (16u * p.v_row_bytes) >> 4;
   const int ksteps = p.qk_ksteps;
-  const bool fp8 = p.qk_is_fp8 != 0;
   // extra K step: ones column x mask column, both K-major without swizzle (8-row groups 128 bytes
   // apart, the second 16-byte half of K in the shared zero block)
   const uint64_t od0 = make_smem_desc(c.smem + p.off_ones, p.off_zero - p.off_ones, 128, 0);
@@ -270,90 +274,98 @@ __device__ void mma_role(const Ctx& c) {
   const uint32_t md_lo = (uint32_t)md0, md_hi = (uint32_t)(md0 >> 32);
   const uint32_t idesc_mask = make_idesc(1u, 1u, 0u, 0u, kTile);
   const bool mask_col = p.mask_col != 0;
+  long long* tl = (p.debug != nullptr && blockIdx.x == 0)
+                      ? reinterpret_cast<long long*>(p.debug + kDbgFloats) + 2 * kDbgTimelineTiles * 8
+                      : nullptr;
+  uint32_t tl_n = 0;
   // ring positions / barrier parities are carried incrementally: no division on this thread
-  uint32_t qk_st = 0, qk_par = 0, pv_st = 0;           // K/V stage of the next QK / PV, kv_full parity
-  uint32_t icount = 0;
-  uint32_t sfree_par0 = 0, sfree_par1 = 0;             // parity of the s_free phase the next QK needs
-  uint32_t qk_first0 = 1, qk_first1 = 1;               // no tile issued on the buffer yet
-  uint32_t pready_par0 = 0, pready_par1 = 0;
+  uint32_t st = 0, kv_par = 0, icount = 0;
+  uint32_t sfree_par[2] = {0, 0}, first[2] = {1, 1};
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
     const Item it = decode_item(p, item);
     const int gv = it.gv;
-    const int nu = p.n_kt * gv;
     AF3K_WAIT(c, BarIdx::q_full, icount & 1);
-    tc_fence_after();
-    int qk_next = 0, pv_next = 0;
-    int qk_s = 0, pv_s = 0, pv_kt = 0;                  // stream of the next QK / PV, key tile of the next PV
-    long long idle_since = 0;
-    uint32_t idle_spins = 0;
-    while (pv_next < nu) {
-      bool progressed = false;
-      if (qk_next < nu) {
-        const int b = qk_s & 1;
-        const bool buf_free = b ? (qk_first1 || mbar_test_wait(bar_addr(c, BarIdx::s_free + 1), sfree_par1))
-                                : (qk_first0 || mbar_test_wait(bar_addr(c, BarIdx::s_free + 0), sfree_par0));
-        if (buf_free && mbar_test_wait(bar_addr(c, BarIdx::kv_full + qk_st), qk_par)) {
-          tc_fence_after();
-          const uint32_t a_lo = qd_lo + qk_s * q_step;
-          const uint32_t b_lo = kd_lo + qk_st * stage_step;
-          const uint32_t s_tmem = c.tmem + kSCol + b * kTile;
+    for (int kt = 0; kt < p.n_kt; ++kt) {
+      for (int s = 0; s < gv; ++s) {
+        const int b = s & 1;
+        // the softmax warpgroup of this buffer must have read the previous logits tile
+        if (b) {
+          if (!first[1]) { AF3K_WAIT(c, BarIdx::s_free + 1, sfree_par[1]); sfree_par[1] ^= 1; }
+          first[1] = 0;
+        } else {
+          if (!first[0]) { AF3K_WAIT(c, BarIdx::s_free + 0, sfree_par[0]); sfree_par[0] ^= 1; }
+          first[0] = 0;
+        }
+        AF3K_WAIT(c, BarIdx::kv_full + st, kv_par);
+        const long long t0 = tl != nullptr ? clock64() : 0;
+        tc_fence_after();
+        const uint32_t a_lo = qd_lo + s * q_step;
+        const uint32_t b_lo = kd_lo + st * stage_step;
+        const uint32_t s_tmem = c.tmem + kSCol + b * kTile;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {     // one K step = 32 bytes of a tile row
-            if (k < ksteps) {
-              if (fp8) mma_ss_f8(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
-              else     mma_ss_f16(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
-            }
+        for (int k = 0; k < 4; ++k) {     // one K step = 32 bytes of a tile row
+          if (k < ksteps) {
+            if (fp8) mma_ss_f8(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
+            else     mma_ss_f16(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
           }
-          if (mask_col) {
-            // start address and leading offset both move with the ring slot: the zero block stays put
-            const uint32_t slot16 = qk_st * (kMaskPanelBytes >> 4);
-            mma_ss_f16(s_tmem, od_lo, od_hi, md_lo + slot16 - (slot16 << 16), md_hi, idesc_mask, 1u);
-          }
-          tc_commit(bar_addr(c, BarIdx::s_full + b));
-          if (b) { if (qk_first1) qk_first1 = 0; else sfree_par1 ^= 1; }
-          else   { if (qk_first0) qk_first0 = 0; else sfree_par0 ^= 1; }
-          if (++qk_st == nkv) { qk_st = 0; qk_par ^= 1; }
-          if (qk_next == nu - 1) tc_commit(bar_addr(c, BarIdx::q_empty));
-          ++qk_next;
-          if (++qk_s == gv) qk_s = 0;
-          progressed = true;
         }
+        if (mask_col) {
+          // start address and leading offset both move with the ring slot: the zero block stays put
+          const uint32_t slot16 = st * (kMaskPanelBytes >> 4);
+          mma_ss_f16(s_tmem, od_lo, od_hi, md_lo + slot16 - (slot16 << 16), md_hi, idesc_mask, 1u);
+        }
+        tc_commit(bar_addr(c, BarIdx::s_full + b));
+        if (kt == p.n_kt - 1 && s == gv - 1) tc_commit(bar_addr(c, BarIdx::q_empty));
+        if (tl != nullptr && tl_n + 2 <= 2 * kDbgTimelineTiles) { tl[tl_n++] = t0; tl[tl_n++] = clock64(); }
+        if (++st == nkv) { st = 0; kv_par ^= 1; }
       }
-      if (pv_next < qk_next) {
-        const int b = pv_s & 1;
-        if (mbar_test_wait(bar_addr(c, BarIdx::p_ready + b), b ? pready_par1 : pready_par0)) {
-          // the previous item's epilogue must have read every O accumulator before the first
-          // P V of this item overwrites one
-          if (pv_next == 0 && icount > 0) AF3K_WAIT(c, BarIdx::epi_done, (icount - 1) & 1);
-          tc_fence_after();
-          const uint32_t b_lo = vd_lo + pv_st * stage_step;
-          const uint32_t o_tmem = c.tmem + kOCol + pv_s * p.nv;
-          const uint32_t p_tmem = c.tmem + kPCol + b * 64;
-          mma_ts_f16(o_tmem, p_tmem, b_lo, vd_hi, idesc_pv, pv_kt > 0 ? 1u : 0u);
+    }
+  }
+}
+
+// O += P V for every tile, in order.
+__device__ void pv_issuer_role(const Ctx& c) {
+  const AttnParams& p = *c.p;
+  const uint32_t nkv = p.kv_stages;
+  const uint32_t v_layout = swizzle_layout_code(p.v_row_bytes);
+  const uint32_t idesc_pv = make_idesc(1u, 1u, 0u, 1u, (uint32_t)p.nv);
+  const uint32_t kv_stage_bytes = p.k_tile_bytes + p.v_tile_bytes;
+  const uint64_t vd0 = make_smem_desc(c.smem + p.off_kv + p.k_tile_bytes, p.v_tile_bytes,
+                                      8 * p.v_row_bytes, v_layout);
+  const uint32_t vd_lo = (uint32_t)vd0, vd_hi = (uint32_t)(vd0 >> 32);
+  const uint32_t stage_step = kv_stage_bytes >> 4;
+  const uint32_t v_kstep = (16u * p.v_row_bytes) >> 4;
+  long long* tl = (p.debug != nullptr && blockIdx.x == 0)
+                      ? reinterpret_cast<long long*>(p.debug + kDbgFloats) + 2 * kDbgTimelineTiles * 8 +
+                            2 * kDbgTimelineTiles
+                      : nullptr;
+  uint32_t tl_n = 0;
+  uint32_t st = 0, icount = 0;
+  uint32_t pready_par[2] = {0, 0};
+  for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
+    const Item it = decode_item(p, item);
+    const int gv = it.gv;
+    for (int kt = 0; kt < p.n_kt; ++kt) {
+      for (int s = 0; s < gv; ++s) {
+        const int b = s & 1;
+        if (b) { AF3K_WAIT(c, BarIdx::p_ready + 1, pready_par[1]); pready_par[1] ^= 1; }
+        else   { AF3K_WAIT(c, BarIdx::p_ready + 0, pready_par[0]); pready_par[0] ^= 1; }
+        // the previous item's epilogue must have read every O accumulator before the first
+        // P V of this item overwrites one
+        if (kt == 0 && s == 0 && icount > 0) AF3K_WAIT(c, BarIdx::epi_done, (icount - 1) & 1);
+        const long long t0 = tl != nullptr ? clock64() : 0;
+        tc_fence_after();
+        const uint32_t b_lo = vd_lo + st * stage_step;
+        const uint32_t o_tmem = c.tmem + kOCol + s * p.nv;
+        const uint32_t p_tmem = c.tmem + kPCol + b * 64;
+        mma_ts_f16(o_tmem, p_tmem, b_lo, vd_hi, idesc_pv, kt > 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 1; k < kTile / 16; ++k)   // 16 keys per step: 8 TMEM columns of P
-            mma_ts_f16(o_tmem, p_tmem + k * 8, b_lo + k * v_kstep, vd_hi, idesc_pv, 1u);
-          tc_commit(bar_addr(c, BarIdx::kv_empty + pv_st));
-          tc_commit(bar_addr(c, BarIdx::pv_done + b));
-          if (b) pready_par1 ^= 1; else pready_par0 ^= 1;
-          if (++pv_st == nkv) pv_st = 0;
-          ++pv_next;
-          if (++pv_s == gv) { pv_s = 0; ++pv_kt; }
-          progressed = true;
-        }
-      }
-      if (progressed) {
-        idle_spins = 0;
-      } else {
-        if (idle_spins == 0) idle_since = clock64();
-        if ((++idle_spins & 63u) == 0u) {
-          if (*c.abort_flag != 0) return;
-          if (clock64() - idle_since > p.wait_limit) {
-            report_timeout(c, pv_next < qk_next ? BarIdx::p_ready + (pv_s & 1) : BarIdx::s_free + (qk_s & 1));
-            return;
-          }
-        }
-        __nanosleep(20);
+        for (int k = 1; k < kTile / 16; ++k)   // 16 keys per step: 8 TMEM columns of P
+          mma_ts_f16(o_tmem, p_tmem + k * 8, b_lo + k * v_kstep, vd_hi, idesc_pv, 1u);
+        // one completion signal: the K/V stage is free, and so are this tile's P buffer and O
+        tc_commit(bar_addr(c, BarIdx::kv_empty + st));
+        if (tl != nullptr && tl_n + 2 <= 2 * kDbgTimelineTiles) { tl[tl_n++] = t0; tl[tl_n++] = clock64(); }
+        if (++st == nkv) st = 0;
       }
     }
     tc_commit(bar_addr(c, BarIdx::item_done));
@@ -369,10 +381,7 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   return v;
 }
 
-// Diagnostic dump: four [128][128] float sections, row = query row of block 0's first tile:
-// raw logits, packed P words (64 used), un-normalised O (nv used), {running max, running sum}.
-constexpr int kDbgS = 0, kDbgP = kTile * kTile, kDbgO = 2 * kTile * kTile, kDbgML = 3 * kTile * kTile,
-              kDbgFloats = 4 * kTile * kTile;
+
 
 // x = s * scale + bias for the 64 columns [kCol0, kCol0 + 64) of the thread's row, row maximum
 // updated.  xr holds the raw logits on entry and x on exit.  Masked and absent keys arrive from
@@ -405,8 +414,9 @@ __device__ __forceinline__ void logits_half(uint32_t (&xr)[kTile], uint32_t bias
 __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, int lane,
                                              uint32_t s_taddr, uint32_t p_taddr, uint32_t o_taddr,
                                              int nv, uint32_t bias_row, uint32_t row7, float scale,
-                                             bool first_kt, bool wait_prev_pv, uint32_t prev_pv_parity,
-                                             float& m_run, float& l_run) {
+                                             bool first_kt, bool wait_prev_pv, int prev_pv_bar,
+                                             uint32_t prev_pv_parity, float& m_run, float& l_run,
+                                             long long* ts = nullptr) {
   uint32_t xr[kTile];
   tmem_ld_x32(s_taddr + 0, &xr[0]);
   tmem_ld_x32(s_taddr + 32, &xr[32]);
@@ -432,6 +442,7 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
   logits_half<64>(xr, bias_row, row7, scale2, mxa, mxb);
 
   const float mt = fmaxf(mxa, mxb);
+  if (ts != nullptr) ts[2] = clock64() + (long long)(mt == 123.456f);   // after the logits pass
   float m_use = m_run;
   float alpha = 1.0f;
   bool need = false;
@@ -444,12 +455,13 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
       alpha = ex2_approx((m_run - mt) * kLog2e);
     }
   }
-  // P buffer and O accumulator are free once the previous P V of this warpgroup has finished
+  // P buffer and O accumulator are free once the previous P V of this warpgroup has finished:
+  // that is the completion that also frees the previous tile's K/V stage
   if (wait_prev_pv) {
-    const bool ok = mbar_wait_bounded(bar_addr(c, BarIdx::pv_done + wg), prev_pv_parity,
-                                      c.p->wait_limit, c.abort_flag);
+    const bool ok = mbar_wait_bounded(bar_addr(c, prev_pv_bar), prev_pv_parity, c.p->wait_limit,
+                                      c.abort_flag);
     if (!__all_sync(0xffffffffu, ok)) {
-      report_timeout(c, BarIdx::pv_done + wg);
+      report_timeout(c, prev_pv_bar);
       return false;
     }
     tc_fence_after();
@@ -465,6 +477,7 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
     }
   }
 
+  if (ts != nullptr) ts[3] = clock64();   // P buffer free, O rescaled
   // p = exp2((x - m) * log2e).  The subtraction comes first so that x == m gives exactly 0 even
   // for the huge negative values of masked keys (a row with no attended key: all weights 1).
   const uint64_t l2e2 = pack_f32x2(kLog2e, kLog2e);
@@ -496,6 +509,7 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
                  : "memory");
   }
   tc_wait_st();
+  if (ts != nullptr) ts[4] = clock64();   // P stored
   float s0, s1, s2, s3;
   unpack_f32x2(suma, s0, s1);
   unpack_f32x2(sumb, s2, s3);
@@ -514,6 +528,10 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
   float* st_m = reinterpret_cast<float*>(__cvta_shared_to_generic(c.smem + p.off_state));
   float* st_l = st_m + kMaxStreams * kTile;
   uint32_t ucnt = 0, bcount = 0, icount = 0;         // tiles done by this warpgroup, bias tiles, items
+  // position of tiles in the CTA-wide order (all streams): gives the K/V stage a tile used
+  uint32_t g_item = 0;                                // tiles of all earlier items
+  uint32_t prev_stage = 0, prev_round = 0;            // stage / ring round of this warpgroup's last tile
+  const uint32_t nkv = p.kv_stages;
 
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
     const Item it = decode_item(p, item);
@@ -529,16 +547,29 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
         float m_run = -INFINITY, l_run = 0.f;
         if (kt > 0) { m_run = st_m[s * kTile + row]; l_run = st_l[s * kTile + row]; }
 
+        // diagnostic timeline (debug build only): SM clock at the phase boundaries of every tile
+        // this warp processes, 8 slots per tile, behind the tile dump
+        long long* ts = nullptr;
+        if (kDebug && p.debug != nullptr && blockIdx.x == 0 && wq == 0 && lane == 0 && ucnt < kDbgTimelineTiles)
+          ts = reinterpret_cast<long long*>(p.debug + kDbgFloats) + ((size_t)wg * kDbgTimelineTiles + ucnt) * 8;
+        if (ts != nullptr) ts[0] = clock64();
         AF3K_WAIT_WARP(c, BarIdx::s_full + wg, ucnt & 1);
         tc_fence_after();
+        if (ts != nullptr) ts[1] = clock64();
         const uint32_t o_taddr = c.tmem + lane_sel + kOCol + s * p.nv;
         float* dbg = nullptr;
         if (kDebug && p.debug != nullptr && blockIdx.x == 0 && icount == 0 && s == 0 && kt == 0)
           dbg = p.debug + (size_t)row * kTile;
         if (!softmax_tile(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row, row & 7, scale,
-                          kt == 0, ucnt > 0, (ucnt - 1) & 1, m_run, l_run))
+                          kt == 0, ucnt > 0, BarIdx::kv_empty + (int)prev_stage, prev_round & 1, m_run,
+                          l_run, ts))
           return;
         ++ucnt;
+        {
+          const uint32_t g = g_item + (uint32_t)(kt * it.gv + s);
+          prev_stage = g % nkv;
+          prev_round = g / nkv;
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::p_ready + wg));
@@ -549,6 +580,8 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
       if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::bias_empty + bst));
       ++bcount;
     }
+
+    g_item += (uint32_t)(p.n_kt * it.gv);
 
     // ---- epilogue: O / l -> bf16 -> global
     AF3K_WAIT_WARP(c, BarIdx::item_done, icount & 1);
@@ -624,7 +657,6 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
       mbar_init(bar_addr(c, BarIdx::s_full + i), 1);
       mbar_init(bar_addr(c, BarIdx::s_free + i), 4);
       mbar_init(bar_addr(c, BarIdx::p_ready + i), 4);
-      mbar_init(bar_addr(c, BarIdx::pv_done + i), 1);
     }
     for (int i = 0; i < kBiasStages; ++i) {
       mbar_init(bar_addr(c, BarIdx::bias_full + i), 1);
@@ -663,7 +695,9 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
     if (warp == 0) {
       if (lane == 0) producer_role(c, &tm_q, &tm_k, &tm_v, &tm_bias);
     } else if (warp == 1) {
-      if (lane == 0) mma_role(c);
+      if (lane == 0) qk_issuer_role(c);
+    } else if (warp == 2) {
+      if (lane == 0) pv_issuer_role(c);
     } else if (warp == 3) {
       if (p.mask_col) mask_writer_role(c, lane);
     }
