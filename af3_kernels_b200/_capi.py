@@ -11,7 +11,8 @@ import os
 from typing import Optional
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libaf3k.so")
+# AF3K_LIBRARY points at another build of the same library (kernel experiments)
+LIB_PATH = os.environ.get("AF3K_LIBRARY") or os.path.join(_HERE, "libaf3k.so")
 
 AF3K_BF16, AF3K_F32, AF3K_FP8_E4M3 = 0, 1, 2
 AF3K_STATUS_WAIT_TIMEOUT = 1
