@@ -4,7 +4,7 @@
 // (src/csrc/dot_product_attention.cpp:88-122: scale -> BRGEMM -> add bias -> add mask ->
 // softmax -> BRGEMM) with one persistent warp-specialised kernel:
 //
-//   warp 0      TMA producer: Q tiles, K/V ring, bias ring (cp.async.bulk.tensor, no multicast)
+//   warp 0      TMA producer: Q tiles, K/V ring, bias ring (cp.async.bulk.tensor, each CTA loads its own tiles)
 //   warp 1      tcgen05.mma issuer for S = Q K^T (smem x smem -> TMEM)
 //   warp 2      TMEM allocator, then tcgen05.mma issuer for O += P V (TMEM x smem -> TMEM)
 //   warp 3      key-mask writer: one bf16 "mask column" per logits tile (see below)

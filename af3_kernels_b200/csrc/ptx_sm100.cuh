@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the attention kernel uses:
-// mbarrier, TMA (cp.async.bulk.tensor, never multicast), tcgen05 MMA / TMEM.
+// mbarrier, TMA (cp.async.bulk.tensor, each CTA loads its own tiles), tcgen05 MMA / TMEM.
 // Every wait in here is bounded; nothing in this file can spin forever.
 #pragma once
 #include <cstdint>
