@@ -1,0 +1,106 @@
+"""Grid (triangle) self-attention modules with the reference's names, constructor arguments and
+parameter names (src/af3_kernels/Attention.py), so that a checkpoint of the reference's modules
+loads unchanged.  The forward passes run on CUDA through ``attention_block``.
+"""
+from __future__ import annotations
+
+import time
+from math import ceil
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .fused_ops import attention_block
+from .tools import pad_to_size, profile, record_comm_time
+
+
+class GridSelfAttentionCpp(nn.Module):
+    """Reference: src/af3_kernels/Attention.py:23-82.  pair [N, N, c_pair], mask [N, N]."""
+
+    def __init__(self, c_pair: int = 128, num_head: int = 4, transpose: bool = False):
+        super().__init__()
+        self.c_pair = c_pair
+        self.num_head = num_head
+        self.qkv_dim = self.c_pair // self.num_head
+        self.transpose = transpose
+        self.act_norm = nn.LayerNorm(self.c_pair)
+        self.pair_bias_projection = nn.Linear(self.c_pair, self.num_head, bias=False)
+        self.q_projection = nn.Linear(self.c_pair, self.c_pair, bias=False)
+        self.k_projection = nn.Linear(self.c_pair, self.c_pair, bias=False)
+        self.v_projection = nn.Linear(self.c_pair, self.c_pair, bias=False)
+        self.gating_query = nn.Linear(self.c_pair, self.c_pair, bias=False)
+        self.output_projection = nn.Linear(self.c_pair, self.c_pair, bias=False)
+
+    def _weights(self):
+        # [in, out] views of the Linear weights: what the reference hands to its operator
+        return (self.q_projection.weight.T, self.k_projection.weight.T, self.v_projection.weight.T,
+                self.gating_query.weight.T, self.output_projection.weight.T)
+
+    def _norm_and_bias(self, pair: torch.Tensor):
+        pair = self.act_norm(pair)
+        bias = self.pair_bias_projection(pair).permute(2, 0, 1)     # [H, N, N]
+        return pair, bias
+
+    @profile("B200 GridSelfAttention")
+    def forward(self, pair: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        pair, bias = self._norm_and_bias(pair)
+        if self.transpose:
+            pair = pair.permute(1, 0, 2)
+        out = attention_block(pair, mask, bias, *self._weights(), self.num_head)
+        if self.transpose:
+            out = out.permute(1, 0, 2)
+        return out
+
+
+class DistributedGridSelfAttentionCpp(GridSelfAttentionCpp):
+    """Reference: src/af3_kernels/Attention.py:85-203.  Every rank holds the whole ``pair`` and
+    computes the rows ``[rank * ceil(N / ws), (rank + 1) * ceil(N / ws))``; the bias is computed
+    redundantly on every rank from the replicated pair, the mask is sliced by row, and the row
+    blocks are all-gathered in ``COMM_SPLIT`` pieces.  The reference overlaps gather *i* with the
+    compute of piece *i + 1* from a helper thread; here the gather runs on a side CUDA stream."""
+
+    def __init__(self, c_pair: int = 128, num_head: int = 4, transpose: bool = False):
+        super().__init__(c_pair, num_head, transpose)
+        self._comm_stream = None
+
+    @profile("B200 Distributed GridSelfAttention")
+    def forward(self, pair: torch.Tensor, mask: torch.Tensor, COMM_SPLIT: int = 4) -> torch.Tensor:
+        rk, ws = dist.get_rank(), dist.get_world_size()
+        seq_len = pair.shape[0]
+        split_size = ceil(seq_len / ws)
+        rows = slice(split_size * rk, split_size * (rk + 1))
+        local_mask = pad_to_size(mask[rows], split_size, 0)
+
+        pair, bias = self._norm_and_bias(pair)
+        bias = bias.contiguous()
+        if self.transpose:
+            pair = pair.permute(1, 0, 2)
+        chunk = pad_to_size(pair[rows], split_size, 0)
+        gathered = torch.empty((ws, split_size, *pair.shape[1:]), device=pair.device, dtype=pair.dtype)
+
+        piece = ceil(split_size / COMM_SPLIT)
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=pair.device)
+        start = time.time()
+        for begin in range(0, split_size, piece):
+            end = min(split_size, begin + piece)
+            out = attention_block(chunk[begin:end], local_mask[begin:end], bias, *self._weights(),
+                                  self.num_head).contiguous()
+            buf = torch.empty((ws, end - begin, *pair.shape[1:]), device=pair.device, dtype=pair.dtype)
+            ready = torch.cuda.Event()
+            ready.record(torch.cuda.current_stream(pair.device))
+            with torch.cuda.stream(self._comm_stream):
+                self._comm_stream.wait_event(ready)
+                dist.all_gather_into_tensor(buf.view(-1, *pair.shape[1:]), out)
+                gathered[:, begin:end].copy_(buf)
+                out.record_stream(self._comm_stream)
+                buf.record_stream(self._comm_stream)
+        torch.cuda.current_stream(pair.device).wait_stream(self._comm_stream)
+        record_comm_time("AG Attn", time.time() - start,
+                         gathered.numel() * gathered.element_size() * (ws - 1) / ws)
+
+        out = gathered.view(ws * split_size, *pair.shape[1:])[:seq_len]
+        if self.transpose:
+            out = out.permute(1, 0, 2)
+        return out.contiguous()

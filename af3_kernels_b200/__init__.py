@@ -1,9 +1,9 @@
 """B200 (sm_100a) drop-in for the attention hot path of HPC-SJTU/af3_kernels.
 
 The public names and signatures follow the reference's ``src/af3_kernels/__init__.py``.  Only
-the biased, key-masked dot-product attention path is implemented (hand-written CUDA behind
-``libaf3k.so``); the reference's other operators are importable but raise
-``NotImplementedError``.  Nothing here computes on the CPU.
+the biased, key-masked dot-product attention path (hand-written CUDA behind ``libaf3k.so``) and
+the two blocks and modules that wrap it are implemented; the reference's unrelated operators
+(GLU / Linear, triangle multiplication) are importable but raise ``NotImplementedError``.  Nothing here computes on the CPU.
 """
 from __future__ import annotations
 
@@ -15,12 +15,18 @@ from . import _capi
 from .dpa import dot_product_attention, read_status
 from .tools import pad_to_size, print_comm_time, profile, record_comm_time
 from .distributed import RowShardedAttention, row_partition
+from .fused_ops import attention_block, self_attention_block
+from .Attention import GridSelfAttentionCpp, DistributedGridSelfAttentionCpp
 
 __all__ = [
     "dot_product_attention_cpp",
     "dot_product_attention",
     "RowShardedAttention",
     "row_partition",
+    "GridSelfAttentionCpp",
+    "DistributedGridSelfAttentionCpp",
+    "attention_block",
+    "self_attention_block",
     "gated_linear_unit_cpp",
     "_attention_cpp",
     "self_attention_cpp",
@@ -68,14 +74,43 @@ def gated_linear_unit_cpp(x, weight, vnni_repacked=False, M_BLK=128, N_BLK=128):
     _not_built("gated_linear_unit_cpp")
 
 
-def _attention_cpp(pair, mask, bias, q_proj, k_proj, v_proj, gating_query, out_proj, head,
-                   use_flash_attention=False, BLK_SZ=128, FLASH_SZ=1024):
-    _not_built("_attention_cpp")
+def _attention_cpp(
+    pair: torch.Tensor,
+    mask: torch.Tensor,
+    bias: torch.Tensor,
+    q_proj: torch.Tensor,
+    k_proj: torch.Tensor,
+    v_proj: torch.Tensor,
+    gating_query: torch.Tensor,
+    out_proj: torch.Tensor,
+    head: int,
+    use_flash_attention: bool = False,  # unused, as in the reference
+    BLK_SZ: int = 128,
+    FLASH_SZ: int = 1024,  # unused, as in the reference
+) -> torch.Tensor:
+    """Grid / triangle self-attention block, same signature as the reference
+    (src/af3_kernels/__init__.py:55-80): q/k/v/gate projections, biased key-masked attention,
+    sigmoid gating, output projection.  Weights are ``[in, out]`` (``linear.weight.T``)."""
+    return attention_block(pair, mask, bias, q_proj, k_proj, v_proj, gating_query, out_proj, head)
 
 
-def self_attention_cpp(pair, mask, bias, q_proj, q_bias, k_proj, v_proj, gating_query, head,
-                       use_flash_attention=False, BLK_SZ=128, FLASH_SZ=1024):
-    _not_built("self_attention_cpp")
+def self_attention_cpp(
+    pair: torch.Tensor,
+    mask: torch.Tensor,
+    bias: torch.Tensor,
+    q_proj: torch.Tensor,
+    q_bias: torch.Tensor,
+    k_proj: torch.Tensor,
+    v_proj: torch.Tensor,
+    gating_query: torch.Tensor,
+    head: int,
+    use_flash_attention: bool = False,  # unused, as in the reference
+    BLK_SZ: int = 128,
+    FLASH_SZ: int = 1024,  # unused, as in the reference
+) -> torch.Tensor:
+    """Single / diffusion attention block over one token sequence, same signature as the
+    reference (src/af3_kernels/__init__.py:83-105): ``pair`` is ``x [N, C]``, ``mask [N]``."""
+    return self_attention_block(pair, mask, bias, q_proj, q_bias, k_proj, v_proj, gating_query, head)
 
 
 def pad_and_align_tensor(x: torch.Tensor, shape, need_init: bool = True, init: float = 0.0,
@@ -96,7 +131,11 @@ def pad_and_align_tensor(x: torch.Tensor, shape, need_init: bool = True, init: f
 
 
 def vnni_repack_tensor(x: torch.Tensor, type: int = 2, BLK_SZ: int = 0) -> torch.Tensor:
-    _not_built("vnni_repack_tensor (a CPU VNNI layout; TMA swizzled tiles replace it on B200)")
+    """The reference re-orders a weight into the VNNI layout of its CPU GEMM
+    (src/csrc/tools.cpp:151-176).  No such layout exists on the GPU (TMA swizzled tiles and cuBLAS
+    take the plain matrix), so the weight is returned unchanged; callers that repack before
+    ``_attention_cpp`` / ``self_attention_cpp`` keep working."""
+    return x
 
 
 def reset_debug_timers():

@@ -188,3 +188,42 @@ def error_stats(out: torch.Tensor, ref: torch.Tensor) -> dict:
         "rel_l1": (d.sum() / r.abs().sum().clamp_min(1e-30)).item(),
         "nan": int(torch.isnan(o).sum().item()),
     }
+
+
+# ----------------------------------------------------------------------------- blocks
+def grid_block_fp32(pair, mask, ln_w, ln_b, w_bias, w_q, w_k, w_v, w_gate, w_out, num_head,
+                    transpose=False, eps=1e-5) -> torch.Tensor:
+    """fp32 restatement of the reference's PyTorch grid self-attention model
+    (examples/grid_self_attention.py:20-96, class AttentionTorch): LayerNorm, pair-bias
+    projection, q/k/v projections, biased key-masked attention, sigmoid gate, output projection.
+    All weights as ``nn.Linear.weight`` ([out, in]).  pair [N, N, C], mask [N, N] -> [N, N, C]."""
+    F = torch.nn.functional
+    x = F.layer_norm(pair.float(), (pair.shape[-1],), ln_w.float(), ln_b.float(), eps)
+    bias = F.linear(x, w_bias.float()).permute(2, 0, 1)
+    if transpose:
+        x = x.permute(1, 0, 2)
+    R, N, C = x.shape
+    D = C // num_head
+    split = lambda t: t.reshape(R, N, num_head, D).permute(0, 2, 1, 3)
+    q, k, v = (split(F.linear(x, w.float())) for w in (w_q, w_k, w_v))
+    o = oracle_fp32(q, k, v, mask, bias)
+    o = o.permute(0, 2, 1, 3).reshape(R, N, C) * torch.sigmoid(F.linear(x, w_gate.float()))
+    out = F.linear(o, w_out.float())
+    return out.permute(1, 0, 2) if transpose else out
+
+
+def self_block_fp32(x, mask, pair_logits, w_q, b_q, w_k, w_v, w_gate, num_head) -> torch.Tensor:
+    """fp32 restatement of the reference's PyTorch single / diffusion attention model
+    (examples/self_attention.py:23-96, class AttentionTorch).  x [N, C], mask [N],
+    pair_logits [H, N, N] -> [N, C]."""
+    F = torch.nn.functional
+    xf = x.float()
+    N, C = xf.shape
+    D = C // num_head
+    split = lambda t: t.reshape(N, num_head, D).permute(1, 0, 2).unsqueeze(0)
+    q = split(F.linear(xf, w_q.float(), b_q.float()))
+    k = split(F.linear(xf, w_k.float()))
+    v = split(F.linear(xf, w_v.float()))
+    o = oracle_fp32(q, k, v, mask, pair_logits)
+    o = o.squeeze(0).permute(1, 0, 2).reshape(N, C)
+    return o * torch.sigmoid(F.linear(xf, w_gate.float()))
