@@ -50,7 +50,7 @@ static inline float bf16_round(float f) {
 static inline float rnd(float f, int round_bf16) { return round_bf16 ? bf16_round(f) : f; }
 
 /* One (batch i, head j, query block kb) task of the non-flash loop (:91-120). */
-static void task_plain(const float* q, const float* k, const float* v, const float* bias,
+static void task_plain(const float* q, const float* kT, const float* v, const float* bias,
                        const float* maskadd, float* out, int S, int K, int M, int BLK, int kb,
                        int rb, float* L, float* qs) {
   const float alpha = rnd(1.0f / sqrtf((float)K), rb); /* ScaleTPP: scalar becomes T first */
@@ -62,12 +62,18 @@ static void task_plain(const float* q, const float* k, const float* v, const flo
   for (int r = 0; r < BLK; ++r) {
     const int qr = r0 + r;
     float* Lr = L + (size_t)r * M;
+    /* logits GEMM: fp32 accumulation over d in index order for every key; kT is K transposed
+     * ([d][key]) so that the loop over keys is the contiguous, vectorisable one */
+    for (int c = 0; c < M; ++c) Lr[c] = 0.f;
+    for (int d = 0; d < K; ++d) {
+      const float qd = qs[r * K + d];
+      const float* kd = kT + (size_t)d * S;
+      for (int c = 0; c < S; ++c) Lr[c] += qd * kd[c];
+    }
+    const float* brow = (qr < S) ? bias + (size_t)qr * S : NULL;
     for (int c = 0; c < M; ++c) {
-      float acc = 0.f;
-      if (c < S)
-        for (int d = 0; d < K; ++d) acc += qs[r * K + d] * k[c * K + d];
-      float x = rnd(acc, rb);                                              /* logits GEMM   */
-      const float b = (qr < S && c < S) ? bias[(size_t)qr * S + c] : 0.f;  /* padded bias=0 */
+      float x = rnd(Lr[c], rb);                                            /* logits GEMM   */
+      const float b = (brow && c < S) ? brow[c] : 0.f;                     /* padded bias=0 */
       x = rnd(x + b, rb);                                                  /* AddTPP        */
       x = rnd(x + maskadd[c], rb);                                         /* AddBiasTPP    */
       Lr[c] = x;
@@ -79,11 +85,15 @@ static void task_plain(const float* q, const float* k, const float* v, const flo
     const float inv = 1.0f / sum;
     for (int c = 0; c < M; ++c) Lr[c] = rnd(Lr[c] * inv, rb);              /* SoftMaxFwdTPP */
     if (qr < S) {
-      for (int d = 0; d < K; ++d) {
-        float acc = 0.f;
-        for (int c = 0; c < S; ++c) acc += Lr[c] * v[c * K + d];           /* padded v = 0  */
-        out[qr * K + d] = rnd(acc, rb);
+      /* P V: accumulation over keys in index order for every d (padded v = 0) */
+      float acc[256];
+      for (int d = 0; d < K; ++d) acc[d] = 0.f;
+      for (int c = 0; c < S; ++c) {
+        const float pc = Lr[c];
+        const float* vc = v + (size_t)c * K;
+        for (int d = 0; d < K; ++d) acc[d] += pc * vc[d];
       }
+      for (int d = 0; d < K; ++d) out[qr * K + d] = rnd(acc[d], rb);
     }
   }
 }
@@ -168,7 +178,9 @@ static void* worker(void* arg) {
   float* L = (float*)malloc(sizeof(float) * (size_t)J->BLK * (J->flash ? J->FLASH : J->M));
   float* qs = (float*)malloc(sizeof(float) * (size_t)J->BLK * J->K);
   float* maskadd = (float*)malloc(sizeof(float) * (size_t)J->M);
-  if (!L || !qs || !maskadd) {
+  float* kT = (float*)malloc(sizeof(float) * (size_t)J->S * J->K);   /* K of one (batch, head), [d][key] */
+  int kT_owner = -1;
+  if (!L || !qs || !maskadd || !kT || J->K > 256) {
     __atomic_store_n(&J->failed, 1, __ATOMIC_RELAXED);
   } else {
     const float neg = rnd(-1e9f, J->rb);
@@ -188,14 +200,22 @@ static void* worker(void* arg) {
       if (J->flash)
         task_flash(J->q + off, J->k + off, J->v + off, bj, maskadd, J->out + off, J->S, J->K,
                    J->M, J->BLK, J->FLASH, kb, J->rb, L, qs);
-      else
-        task_plain(J->q + off, J->k + off, J->v + off, bj, maskadd, J->out + off, J->S, J->K,
+      else {
+        if (kT_owner != t / J->Mb) {
+          const float* ksrc = J->k + off;
+          for (int c = 0; c < J->S; ++c)
+            for (int d = 0; d < J->K; ++d) kT[(size_t)d * J->S + c] = ksrc[(size_t)c * J->K + d];
+          kT_owner = t / J->Mb;
+        }
+        task_plain(J->q + off, kT, J->v + off, bj, maskadd, J->out + off, J->S, J->K,
                    J->M, J->BLK, kb, J->rb, L, qs);
+      }
     }
   }
   free(L);
   free(qs);
   free(maskadd);
+  free(kT);
   return NULL;
 }
 

@@ -274,3 +274,44 @@ def test_launch_count(cuda_device):
     dot_product_attention(q, q, q, None, torch.zeros(1, 64, 64, device=cuda_device, dtype=torch.bfloat16))
     assert lib.af3k_last_launch_count() == 1
     assert read_status(cuda_device)[0] == 0
+
+
+def test_debug_dump_shows_the_tensor_core_stages(cuda_device):
+    """The diagnostic build dumps the first logits tile: raw Q K^T (+ mask column), P as written to
+    TMEM, the un-normalised accumulator and the row statistics.  Checking each against plain fp32
+    math pins the operand layouts (swizzled K-major Q/K, MN-major V, P in TMEM, mask column)."""
+    dev = cuda_device
+    lib = _capi.load()
+    g = torch.Generator().manual_seed(21)
+    S, D = 128, 32
+    q = torch.randn(1, 1, S, D, generator=g).to(torch.bfloat16).to(dev)
+    k = torch.randn(1, 1, S, D, generator=g).to(torch.bfloat16).to(dev)
+    v = torch.randn(1, 1, S, D, generator=g).to(torch.bfloat16).to(dev)
+    bias = torch.randn(1, S, S, generator=g).to(torch.bfloat16).to(dev)
+    mask = torch.rand(S, generator=g) >= 0.2
+    mask[0] = True
+    timeline_floats = 2 * (2 * 256 * 8 + 4 * 256)
+    dump = torch.zeros(4 * 128 * 128 + timeline_floats, dtype=torch.float32, device=dev)
+    lib.af3k_debug_set_dump(dump.data_ptr())
+    try:
+        out = dot_product_attention(q, k, v, mask.to(dev), bias, check_status=True)
+    finally:
+        lib.af3k_debug_set_dump(None)
+    d = dump[: 4 * 128 * 128].view(4, 128, 128).cpu()
+    s_ref = q[0, 0].float().cpu() @ k[0, 0].float().cpu().T
+    keep = mask[None, :].expand(S, S)
+    assert (d[0][keep] - s_ref[keep]).abs().max().item() <= 1e-4          # attended keys: q . k
+    assert (d[0][~keep] == -(2.0 ** 47)).all()                             # masked keys: exactly -2^47
+    p_words = d[1][:, :64].contiguous().view(torch.int32)
+    p_lo = (p_words << 16).view(torch.float32)
+    p_hi = (p_words & -65536).view(torch.float32)
+    p = torch.stack([p_lo, p_hi], dim=-1).reshape(S, S)                    # key 2c in the low half
+    x = s_ref * D ** -0.5 + bias[0].float().cpu()
+    x = x.masked_fill(~keep, float("-inf"))
+    p_ref = torch.exp(x - x.max(dim=1, keepdim=True).values)
+    assert (p - p_ref).abs().max().item() <= 8e-3                          # bf16 rounding of P
+    o_ref = p @ v[0, 0].float().cpu()
+    assert (d[2][:, :D] - o_ref).abs().max().item() <= 1e-3
+    assert (d[3][:, 1] - p_ref.sum(dim=1)).abs().max().item() <= 2e-2 * p_ref.sum(dim=1).max().item()
+    ref = O.oracle_fp32(q.cpu(), k.cpu(), v.cpu(), mask, bias.cpu())
+    _check_bf16(out.cpu(), ref, "debug build")
