@@ -181,7 +181,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg2", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"])
+    ap.add_argument("--workload", default="cfg2",
+                    choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "grid_block"])
     ap.add_argument("--rows", type=int, default=0, help="override pair rows per GPU (debugging)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel-only", action="store_true",
@@ -211,6 +212,13 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     name = args.workload
+    if name == "grid_block":
+        if rank == 0:
+            grid_block_line(args, dev)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     c = dict(O.CONFIGS[name])
     if args.rows:
         c["B1"] = args.rows
@@ -382,6 +390,37 @@ def main():
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def grid_block_line(args, dev):
+    """Extra workload (not the headline line): the whole grid self-attention module at N = 768,
+    c_pair = 128, 4 heads - LayerNorm, bias and q/k/v/gate projections (cuBLAS), the attention
+    kernel, gating and output projection - on a device-resident pair representation."""
+    import af3_kernels_b200 as A
+    N, C, H = (args.rows or 768), 128, 4
+    torch.manual_seed(0)
+    m = A.GridSelfAttentionCpp(C, H).to(dev).to(torch.bfloat16).eval()
+    pair = torch.randn(N, N, C, device=dev, dtype=torch.bfloat16)
+    mask = torch.rand(N, N, device=dev) >= 0.05
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            m(pair, mask)
+        torch.cuda.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in range(args.steps)]
+        for e0, e1 in evs:
+            e0.record()
+            m(pair, mask)
+            e1.record()
+        torch.cuda.synchronize()
+    ms = sum(e0.elapsed_time(e1) for e0, e1 in evs) / len(evs)
+    attn_flops = 4.0 * N * H * N * N * (C // H)
+    gemm_flops = 2.0 * N * N * C * (5 * C + H)
+    print(json.dumps({"metric": "grid_block_tflops", "value": (attn_flops + gemm_flops) / (ms / 1e3) / 1e12,
+                      "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+                      "ms_per_step": ms, "attention_flops": attn_flops, "projection_flops": gemm_flops,
+                      "config": {"workload": f"GridSelfAttentionCpp forward, pair [{N},{N},{C}] bf16, {H} heads"},
+                      "dtype": "bf16", "data": "synthetic"}), flush=True)
 
 
 # DRAM bytes per launch of attention_kernel from one ncu capture (dram__bytes_read.sum +
