@@ -4,7 +4,6 @@
 
 #include <atomic>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -87,10 +86,11 @@ int device_info(DeviceInfo** out) {
   if (!d.attr_set) {
     // the opt-in limit covers static + dynamic shared memory; the kernel has a few static bytes
     const int dyn = d.max_smem_optin - kStaticSmemReserve;
-    if ((e = cudaFuncSetAttribute(attention_kernel<false>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dyn)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(attention_kernel<true>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dyn)) != cudaSuccess)
+    const cudaFuncAttribute attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+    if ((e = cudaFuncSetAttribute(attention_kernel<false, false>, attr, dyn)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(attention_kernel<false, true>, attr, dyn)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(attention_kernel<true, false>, attr, dyn)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(attention_kernel<true, true>, attr, dyn)) != cudaSuccess)
       return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize)", e);
     d.attr_set = true;
   }
@@ -123,7 +123,7 @@ int validate(const af3k_attention_desc& d) {
   if (d.qk_dtype == AF3K_FP8_E4M3 && d.D % 16 != 0) return AF3K_ERR_BAD_SHAPE;
   if (d.B1 > 0x7fffffff || d.B2 > 0x7fffffff || d.Sq > 0x7fffff00 || d.Sk > 0x7fffff00)
     return AF3K_ERR_BAD_SHAPE;
-  if (d.rows_per_item < 0 || d.rows_per_item > kMaxStreams) return AF3K_ERR_BAD_SHAPE;
+  if (d.rows_per_item < 0 || d.rows_per_item > 8) return AF3K_ERR_BAD_SHAPE;   // a request, clamped by the plan
   const int64_t es = d.qk_dtype == AF3K_FP8_E4M3 ? 1 : 2;
   for (int i = 0; i < 3; ++i) {
     if (d.q_stride[i] < 0 || d.k_stride[i] < 0 || d.v_stride[i] < 0 || d.out_stride[i] < 0)
@@ -145,9 +145,7 @@ struct Plan {
   int grid;
 };
 
-// Picks rows-per-item G and the K/V ring depth.  Cost model: a CTA's time is proportional to the
-// softmax slots it processes (rounds x G, G rounded up to even); a staged bias tile is amortised
-// over G streams.
+// Picks rows-per-item G and the K/V ring depth from a cost model of one CTA's time (below).
 int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
   AttnParams& p = plan->p;
   std::memset(&p, 0, sizeof(p));
@@ -167,8 +165,9 @@ int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
 
   const int budget = dev.max_smem_optin - 1024 /*alignment slack*/ - kStaticSmemReserve;
   p.mask_col = 1;   // set for real in the launch path once the mask pointer is known
-  const int fixed = kBiasStages * kBiasTileBytes + kMaxStreams * kTile * 8 + 256 /*barriers*/ +
-                    (kMaxKvStages + 2) * (int)kMaskPanelBytes /*ones column, mask ring, zero block*/;
+  const int fixed = kBiasStages * kBiasTileBytes + kMaxStreams * kTile * 8 + (int)kBarrierBlockBytes +
+                    (kMaxKvStages + 2) * (int)kMaskPanelBytes /*ones column, mask ring, zero block*/ +
+                    (int)kIdentBytes;
   const int kv_stage = (int)(p.k_tile_bytes + p.v_tile_bytes);
   const int g_tmem = (int)((kTmemCols - kOCol) / p.nv);
   int g_max = kMaxStreams < g_tmem ? kMaxStreams : g_tmem;
@@ -180,16 +179,21 @@ int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
   const int g_req = d.rows_per_item > g_max ? g_max : d.rows_per_item;
   for (int g = 1; g <= g_max; ++g) {
     if (g_req != 0 && g != g_req) continue;
-    int stages = (budget - fixed - g * (int)p.q_tile_bytes) / kv_stage;
+    int stages = (budget - fixed - 2 * g * (int)p.q_tile_bytes) / kv_stage;   // Q tiles are double-buffered
     if (stages > kMaxKvStages) stages = kMaxKvStages;
     if (stages < 2) continue;
     const long long groups = (p.B1 + g - 1) / g;
     const long long items = groups * p.B2 * p.n_qt;
     const long long rounds = (items + dev.sm_count - 1) / dev.sm_count;
-    // streams alternate between the two softmax warpgroups: an odd count leaves one idle slot
+    // streams alternate between the two softmax warpgroups: an odd count leaves one idle slot.
+    // A CTA's time, in logits-tile times of one warpgroup: per item n_kt tiles for each of its
+    // slots / 2 streams plus about 0.8 for the epilogue and the hand-over to the next item.
     const int slots = (g & 1) ? g + 1 : g;
-    double cost = (double)rounds * slots * (1.0 + 0.3 / g);
-    if (stages < 3) cost *= 1.15;
+    double cost = (double)rounds * (p.n_kt * (slots / 2) + 0.8);
+    // a K/V tile takes about two thousand cycles to arrive, most of a logits tile's time: with a
+    // short ring the MMAs wait for their operands (measured: 4 stages cost about 3 %)
+    static const double kRingPenalty[7] = {0, 0, 1.4, 1.15, 1.03, 1.0, 1.0};
+    cost *= kRingPenalty[stages];
     if (best_g == 0 || cost < best_cost) { best_g = g; best_cost = cost; best_stages = stages; }
   }
   if (best_g == 0) return AF3K_ERR_BAD_SHAPE;
@@ -201,14 +205,15 @@ int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
   p.n_items = (int)items;
 
   uint32_t off = 0;
-  p.off_q = off;      off += p.G * p.q_tile_bytes;
+  p.off_q = off;      off += 2 * p.G * p.q_tile_bytes;
   p.off_kv = off;     off += p.kv_stages * kv_stage;
   p.off_bias = off;   off += kBiasStages * kBiasTileBytes;
   p.off_state = off;  off += kMaxStreams * kTile * 8;
-  p.off_bar = off;    off += 256;
+  p.off_bar = off;    off += kBarrierBlockBytes;
   p.off_ones = off;   off += kMaskPanelBytes;
   p.off_mcol = off;   off += kMaxKvStages * kMaskPanelBytes;
   p.off_zero = off;   off += kMaskPanelBytes;
+  p.off_ident = off;  off += kIdentBytes;
   size_t smem = off + 1024;
   // One CTA per SM is required (each CTA allocates all of TMEM): ask for more than half the SM's
   // shared memory even when the tiles need less.
@@ -407,10 +412,18 @@ int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, c
   p.wait_limit = wait_limit_cycles();
 
   p.debug = g_debug_dump.load();
-  if (p.debug != nullptr)
-    attention_kernel<true><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
+  // bf16 q/k: scale, bias and mask all come out of the tensor core; fp8 q/k: the softmax threads
+  // apply the (inexact-in-bf16) de-quantisation scale and the bias in fp32
+  const bool tc_bias = !p.qk_is_fp8;
+  const bool dbg = p.debug != nullptr;
+  if (dbg && tc_bias)
+    attention_kernel<true, true><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
+  else if (dbg)
+    attention_kernel<true, false><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
+  else if (tc_bias)
+    attention_kernel<false, true><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
   else
-    attention_kernel<false><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
+    attention_kernel<false, false><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("launch attention_kernel", e);
   ++launches;

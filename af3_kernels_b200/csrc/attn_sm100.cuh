@@ -5,9 +5,9 @@
 // softmax -> BRGEMM) with one persistent warp-specialised kernel:
 //
 //   warp 0      TMA producer: Q tiles, K/V ring, bias ring (cp.async.bulk.tensor, each CTA loads its own tiles)
-//   warp 1      tcgen05.mma issuer for S = Q K^T (smem x smem -> TMEM)
-//   warp 2      TMEM allocator, then tcgen05.mma issuer for O += P V (TMEM x smem -> TMEM)
-//   warp 3      key-mask writer: one bf16 "mask column" per logits tile (see below)
+//   warp 1      tcgen05.mma issuer for the logits (smem x smem -> TMEM)
+//   warp 2      TMEM allocator, then tcgen05.mma issuer for O += P V (TMEM x smem -> TMEM); Q scaler
+//   warp 3      key-mask writer (see below)
 //   warps 4-7   softmax warpgroup 0 (owns S / P buffer 0 and the even streams of a work item)
 //   warps 8-11  softmax warpgroup 1 (owns S / P buffer 1 and the odd streams)
 //
@@ -16,18 +16,30 @@
 // Q tile, K/V tiles, fp32 running max / sum and O accumulator in TMEM.  One softmax thread owns
 // one query row (TMEM lane), so row max / row sum need no cross-thread traffic.
 //
-// The key mask costs the softmax threads nothing: the first GEMM gets one extra K step whose A
-// operand is a constant column of ones and whose B operand holds, per key, 0 (attend), -2^47
-// (masked) or -inf (beyond the sequence).  The tensor core adds that value to every logit of the
-// key's column, so a masked key ends up with weight exactly 0, a row whose keys are all masked
-// with uniform weights over its real keys (what "fill with -1e9, then softmax" gives), and a key
-// that does not exist with weight 0 always.
+// The softmax threads are the bottleneck of this operator (one exponential per logit on the
+// 16-lane XU, every other instruction competing for the same issue slots), so everything that
+// can be an MMA is one.  With bf16 q/k the whole logit comes out of the tensor core:
+//
+//   * scale: warp 2 multiplies each Q tile by the softmax scale in shared memory and rounds it
+//     back to bf16 - the reference's own first step (q = q * scaling, in bf16);
+//   * bias: eight small MMAs per tile (M = 128, N = 16, K = 16) whose A operand is a 16-key
+//     slice of the staged bf16 bias tile and whose B operand is a 16 x 16 identity, each adding
+//     its slice into 16 columns of the accumulator - exact, the products are bias x 1;
+//   * key mask: one more K step whose A operand is a column of ones and whose B operand holds,
+//     per key, 0 (attend), -2^47 (masked) or -inf (beyond the sequence).  A masked key ends up
+//     with weight exactly 0, a row whose keys are all masked with uniform weights over its real
+//     keys (what "fill with -1e9, then softmax" gives), a key that does not exist with weight 0.
+//
+// What is left per logit is a maximum, one fused multiply-add, the exponential, the row sum and
+// the bf16 rounding of P.  With fp8 q/k the de-quantisation factors are not exact in bf16, so
+// scale and bias are applied by the softmax threads in fp32 (the bias tile is read from shared
+// memory); the mask column is used either way.
 //
 // Logits stay fp32 from the tensor core to the exponential; P is rounded to bf16 once, when it
 // is written to TMEM as the A operand of the second GEMM.  S and P live in separate TMEM columns:
-// a warpgroup releases its S buffer as soon as the logits are in registers, so the next Q K^T of
-// that buffer runs under the softmax of the current tile.  O is rescaled lazily: only when a row
-// maximum grows by more than 2^8 (exact, because l is scaled with it).
+// a warpgroup releases its S buffer as soon as the logits are in registers, so the next logits
+// tile of that buffer is computed under the softmax of the current one.  O is rescaled lazily:
+// only when a row maximum grows by more than 2^8 (exact, because l is scaled with it).
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -42,7 +54,7 @@ constexpr int kTile = 128;         // query rows per tile == keys per tile
 constexpr int kThreads = 384;      // 12 warps
 // 65536 registers per SM: launched at 168 per thread, then 128 x 56 + 256 x 224 = 64512
 constexpr int kRegsMisc = 56, kRegsSoftmax = 224;
-constexpr int kMaxStreams = 8;     // pair rows per work item (TMEM: kOCol + G * nv <= 512 columns)
+constexpr int kMaxStreams = 4;     // pair rows per work item (TMEM: kOCol + G * nv <= 512 columns)
 // TMEM columns: two fp32 logits buffers, two bf16 P buffers (two keys per column), then O.
 constexpr uint32_t kSCol = 0, kPCol = 2 * 128, kOCol = 2 * 128 + 2 * 64;
 constexpr float kLazyRescaleLog2 = 8.0f;   // keep a stale row max while exp2 arguments stay <= 8
@@ -55,6 +67,8 @@ constexpr uint32_t kTmemCols = 512;
 // row are equal (uniform weights when nothing else is left) and vanish next to any real key.
 constexpr uint16_t kMaskColKeep = 0x0000, kMaskColMasked = 0xD700, kMaskColAbsent = 0xFF80;
 constexpr uint32_t kMaskPanelBytes = 2048;   // 128 keys x one 16-byte core-matrix row
+constexpr uint32_t kBarrierBlockBytes = 512;
+constexpr uint32_t kIdentBytes = 512;        // 16 x 16 bf16 identity, K-major core matrices
 constexpr float kLog2e = 1.4426950408889634f;
 
 enum StatusBits : int {
@@ -89,22 +103,27 @@ struct AttnParams {
   //   off_ones: A operand, element (row, 0) = 1;  off_mcol: ring of per-tile B operands, element
   //   (key, 0) = mask value;  off_zero: the all-zero second half of K shared by both.
   uint32_t off_ones, off_mcol, off_zero;
+  uint32_t off_ident;    // 16 x 16 identity (B operand of the bias MMAs)
   int mask_col;          // 1: the extra K step runs (a mask was given or Sk is not a tile multiple)
 };
 
-// Barrier slots inside the barrier block (8 bytes each).
+// Barrier slots inside the barrier block (8 bytes each, kBarrierBlockBytes in all).
 struct BarIdx {
-  static constexpr int q_full = 0, q_empty = 1, item_done = 2, epi_done = 3;
-  static constexpr int s_full = 4;      // [2]  Q K^T of a tile finished
-  static constexpr int s_free = 6;      // [2]  softmax warpgroup has the logits in registers
-  static constexpr int p_ready = 8;     // [2]  P written (and O rescaled if needed)
-  // (slots 10, 11 unused)  P V completion is signalled on the tile's kv_empty barrier
-  static constexpr int bias_full = 12;  // [kBiasStages]
-  static constexpr int bias_empty = 14; // [kBiasStages]
-  static constexpr int kv_full = 16;    // [kMaxKvStages]
-  static constexpr int kv_empty = 16 + kMaxKvStages;
-  static constexpr int count = 16 + 2 * kMaxKvStages;
+  static constexpr int s_full = 0;      // [2]  logits of a tile finished
+  static constexpr int s_free = 2;      // [2]  softmax warpgroup has the logits in registers
+  static constexpr int p_ready = 4;     // [2]  P written (and O rescaled if needed)
+  static constexpr int epi_done = 6;    // [2]  warpgroup has read its O accumulators of the item
+  static constexpr int bias_full = 8;   // [kBiasStages]
+  static constexpr int bias_empty = 10; // [kBiasStages]
+  static constexpr int kv_full = 12;    // [kMaxKvStages]
+  static constexpr int kv_empty = 12 + kMaxKvStages;       // P V of the stage's tile finished
+  // Q tiles are double-buffered by item: slot = (item parity) * kMaxStreams + stream
+  static constexpr int q_full = 12 + 2 * kMaxKvStages;       // [2 * kMaxStreams]  Q tile landed
+  static constexpr int q_empty = q_full + 2 * kMaxStreams;   // [2 * kMaxStreams]  last Q K^T of the stream finished
+  static constexpr int q_scaled = q_empty + 2 * kMaxStreams; // [2 * kMaxStreams]  warp 3 has scaled the Q tile
+  static constexpr int count = q_scaled + 2 * kMaxStreams;
 };
+static_assert(BarIdx::count * 8 <= (int)kBarrierBlockBytes, "barrier block too small");
 
 // Diagnostic dump: four [128][128] float sections, row = query row of block 0's first tile:
 // raw logits, packed P words (64 used), un-normalised O (nv used), {running max, running sum}.
@@ -139,6 +158,16 @@ __device__ __noinline__ void report_timeout(const Ctx& c, int bar_idx) {
                            (ctx).abort_flag)) {                                              \
       report_timeout(ctx, idx);                                                              \
       return;                                                                                \
+    }                                                                                        \
+  } while (0)
+
+// Form for helpers that report failure through their return value.
+#define AF3K_WAIT_NORET(ctx, idx, parity)                                                    \
+  do {                                                                                       \
+    if (!mbar_wait_bounded(bar_addr(ctx, idx), (parity), (ctx).p->wait_limit,                \
+                           (ctx).abort_flag)) {                                              \
+      report_timeout(ctx, idx);                                                              \
+      return false;                                                                          \
     }                                                                                        \
   } while (0)
 
@@ -178,13 +207,25 @@ __device__ void producer_role(const Ctx& c, const CUtensorMap* tm_q, const CUten
   const AttnParams& p = *c.p;
   uint32_t ucount = 0, bcount = 0, icount = 0;
   const uint32_t nkv = p.kv_stages;
+  // Q tiles of item j live in buffer j & 1; the tiles of the next item are requested while the
+  // current item runs, so that they are in place (and scaled) when it ends.
+  auto load_q = [&](const Item& it, uint32_t j) {
+    const uint32_t buf = j & 1;
+    for (int s = 0; s < it.gv; ++s) {
+      const int slot = (int)buf * kMaxStreams + s;
+      // the buffer's previous user (item j - 2) must have finished its last Q K^T of this stream
+      if (j >= 2) AF3K_WAIT_NORET(c, BarIdx::q_empty + slot, ((j >> 1) - 1) & 1);
+      mbar_arrive_expect_tx(bar_addr(c, BarIdx::q_full + slot), p.q_tile_bytes);
+      tma_load_4d(c.smem + p.off_q + (buf * p.G + s) * p.q_tile_bytes, tm_q, bar_addr(c, BarIdx::q_full + slot),
+                  0, it.qt * kTile, it.h, it.r0 + s);
+    }
+    return true;
+  };
+  if ((int)blockIdx.x < p.n_items) {
+    if (!load_q(decode_item(p, blockIdx.x), 0)) return;
+  }
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
     const Item it = decode_item(p, item);
-    if (icount > 0) AF3K_WAIT(c, BarIdx::q_empty, (icount - 1) & 1);
-    mbar_arrive_expect_tx(bar_addr(c, BarIdx::q_full), it.gv * p.q_tile_bytes);
-    for (int s = 0; s < it.gv; ++s)
-      tma_load_4d(c.smem + p.off_q + s * p.q_tile_bytes, tm_q, bar_addr(c, BarIdx::q_full), 0,
-                  it.qt * kTile, it.h, it.r0 + s);
     for (int kt = 0; kt < p.n_kt; ++kt) {
       const uint32_t bst = bcount % kBiasStages;
       if (bcount >= kBiasStages)
@@ -205,36 +246,124 @@ __device__ void producer_role(const Ctx& c, const CUtensorMap* tm_q, const CUten
         tma_load_4d(kdst + p.k_tile_bytes, tm_v, full, 0, kt * kTile, it.h, it.r0 + s);
         ++ucount;
       }
+      if (kt == 0 && item + (int)gridDim.x < p.n_items) {
+        if (!load_q(decode_item(p, item + gridDim.x), icount + 1)) return;
+      }
     }
   }
 }
 
-// ------------------------------------------------------------------ key-mask writer (one warp)
-// For every logits tile, in the producer's order: 128 mask values (bf16) into the tile's slot of
-// the mask-column ring.  The slot is the B operand of the extra K step; only element 0 of each
-// key's 16-byte row changes, the rest stays zero.  Arrives on the tile's kv_full barrier (which
-// then counts two arrivals: this one and the producer's).
+// ------------------------------------------------------------------ Q scaling and key-mask column
+// q <- bf16(q * scale) for 1 KB of a Q tile in shared memory, 32 bytes per lane (any swizzle: the
+// operation is elementwise).
+__device__ __forceinline__ void scale_q_chunk(uint32_t addr, float scale, int lane) {
+  uint32_t w[8];
+  const uint32_t a = addr + lane * 16;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(a));
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(a + 512));
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+    w[e] = pack_bf16x2(__uint_as_float(w[e] << 16) * scale, __uint_as_float(w[e] & 0xffff0000u) * scale);
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]) : "memory");
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a + 512), "r"(w[4]), "r"(w[5]),
+               "r"(w[6]), "r"(w[7]) : "memory");
+}
+
+// The 128 mask-column values (bf16) of one logits tile, four per lane.
+__device__ __forceinline__ void mask_values(const AttnParams& p, const Item& it, int kt, int s, int lane,
+                                            uint16_t (&val)[4]) {
+  const uint8_t* mrow = p.mask != nullptr ? p.mask + (long long)(it.r0 + s) * p.mask_row_stride : nullptr;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int key = kt * kTile + 32 * g + lane;
+    val[g] = key >= p.Sk ? kMaskColAbsent
+                         : ((mrow == nullptr || mrow[key] != 0) ? kMaskColKeep : kMaskColMasked);
+  }
+}
+
+// Scaling of Q tiles, cut into 1 KB pieces so that the warp doing it (the P V issuer, which
+// mostly waits) can fit the pieces into its waiting time.  Tiles of item j live in Q buffer
+// j & 1 and land while item j - 1 runs.
+struct QScaler {
+  uint32_t item = 0, chunk = 0;   // item index (per CTA) of the tiles being scaled, next piece
+  int gv = 0, tile = 0;           // tiles that item has, next tile
+  __device__ __forceinline__ void start(uint32_t j, int n) { item = j; gv = n; tile = 0; chunk = 0; }
+  __device__ __forceinline__ bool pending() const { return tile < gv; }
+  // One piece.  block: wait (bounded) for the tile to land, else give up if it has not.
+  // Returns 1 = did a piece, 0 = nothing to do (now), -1 = a wait ran out.
+  __device__ __forceinline__ int step(const Ctx& c, int lane, bool block) {
+    const AttnParams& p = *c.p;
+    if (tile >= gv) return 0;
+    const uint32_t buf = item & 1;
+    const int slot = (int)buf * kMaxStreams + tile;
+    if (chunk == 0) {
+      const uint32_t par = (item >> 1) & 1;
+      bool ok = mbar_test_wait(bar_addr(c, BarIdx::q_full + slot), par);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (!block) return 0;
+        ok = mbar_wait_bounded(bar_addr(c, BarIdx::q_full + slot), par, p.wait_limit, c.abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) {
+          report_timeout(c, BarIdx::q_full + slot);
+          return -1;
+        }
+      }
+    }
+    scale_q_chunk(c.smem + p.off_q + (buf * p.G + tile) * p.q_tile_bytes + (chunk << 10), p.scale, lane);
+    if (++chunk == (p.q_tile_bytes >> 10)) {
+      fence_proxy_async_smem();    // make the generic-proxy stores visible to the tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::q_scaled + slot));
+      chunk = 0;
+      ++tile;
+    }
+    return 1;
+  }
+};
+
+// Waits for a barrier phase; while it is pending, does Q scaling pieces (if any are left).
+#define AF3K_WAIT_WARP_OR_SCALE(ctx, idx, parity, scaler, lane)                              \
+  do {                                                                                       \
+    while (true) {                                                                           \
+      const bool done_ = mbar_test_wait(bar_addr(ctx, idx), (parity));                       \
+      if (__all_sync(0xffffffffu, done_)) break;                                             \
+      const int r_ = (scaler).step(ctx, lane, false);                                        \
+      if (r_ < 0) return;                                                                    \
+      if (r_ == 0) {                                                                         \
+        AF3K_WAIT_WARP(ctx, idx, parity);                                                    \
+        break;                                                                               \
+      }                                                                                      \
+    }                                                                                        \
+  } while (0)
+
+// Key-mask writer (one warp).  For every logits tile, in the producer's order: write the tile's
+// 128 mask values into its slot of the mask-column ring.  The slot is the B operand of the extra
+// K step; only element 0 of each key's 16-byte row changes, the rest stays zero.  Arrives on the
+// tile's kv_full barrier (which then counts two arrivals: this one and the producer's).  The mask
+// bytes of a tile are requested one tile ahead, so their latency is not on the path.
 __device__ void mask_writer_role(const Ctx& c, int lane) {
   const AttnParams& p = *c.p;
   const uint32_t nkv = p.kv_stages;
-  uint32_t st = 0, round = 0;      // ring slot and how many times the ring wrapped
+  uint32_t st = 0, round = 0;      // ring slot, how many times the ring wrapped
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x) {
     const Item it = decode_item(p, item);
+    uint16_t val[4];
+    mask_values(p, it, 0, 0, lane, val);
     for (int kt = 0; kt < p.n_kt; ++kt) {
       for (int s = 0; s < it.gv; ++s) {
-        uint16_t val[4];
-        const uint8_t* mrow = p.mask != nullptr ? p.mask + (long long)(it.r0 + s) * p.mask_row_stride : nullptr;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int key = kt * kTile + 32 * g + lane;
-          val[g] = key >= p.Sk ? kMaskColAbsent
-                               : ((mrow == nullptr || mrow[key] != 0) ? kMaskColKeep : kMaskColMasked);
+        const uint16_t cur[4] = {val[0], val[1], val[2], val[3]};
+        {
+          const int ns = s + 1 < it.gv ? s + 1 : 0;
+          const int nkt = s + 1 < it.gv ? kt : kt + 1;
+          if (nkt < p.n_kt) mask_values(p, it, nkt, ns, lane, val);
         }
         if (round > 0) AF3K_WAIT_WARP(c, BarIdx::kv_empty + st, (round - 1) & 1);
         const uint32_t slot = c.smem + p.off_mcol + st * kMaskPanelBytes;
 #pragma unroll
         for (int g = 0; g < 4; ++g)
-          asm volatile("st.shared.u16 [%0], %1;" ::"r"(slot + (32 * g + lane) * 16), "h"(val[g]) : "memory");
+          asm volatile("st.shared.u16 [%0], %1;" ::"r"(slot + (32 * g + lane) * 16), "h"(cur[g]) : "memory");
         fence_proxy_async_smem();    // make the generic-proxy stores visible to the tensor core
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::kv_full + st));
@@ -244,16 +373,21 @@ __device__ void mask_writer_role(const Ctx& c, int lane) {
   }
 }
 
-// ------------------------------------------------------------------ MMA issuers (two threads)
-// Issuing a tcgen05.mma costs its thread tens to hundreds of cycles, and the tiles here are small
-// (N = 128, K = 16 and N = D, K = 16), so one thread issuing both GEMMs of every tile was the
-// limiter of the whole kernel.  The two GEMMs are therefore issued by two threads in two warps:
-// they touch different TMEM columns and every hand-over between them goes through an mbarrier,
-// so no ordering between the two instruction streams is assumed.
+// ------------------------------------------------------------------ MMA issuers (two warps)
+// The tiles here are small (N = 128, K = 16 and N = D, K = 16), so the cost of issuing an MMA
+// matters: one thread issuing both GEMMs of every tile was the limiter of the whole kernel, and
+// so was issuing from one lane of a diverged warp (about 150 cycles per tcgen05.mma, because the
+// descriptors then travel through per-lane registers).  The two GEMMs are therefore issued by two
+// warps, each running its control flow and its waits as a whole warp so that addresses and
+// descriptors stay warp-uniform; one elected lane issues.  The two warps touch different TMEM
+// columns and every hand-over between them goes through an mbarrier, so no ordering between the
+// two instruction streams is assumed.
 
-// S = Q K^T (+ mask column) for every tile, in order.
+// Logits of every tile, in order: Q K^T, then the mask column, then (bf16 q/k) the bias slices.
+template <bool kTcBias>
 __device__ void qk_issuer_role(const Ctx& c) {
   const AttnParams& p = *c.p;
+  const bool leader = elect_one();
   const uint32_t nkv = p.kv_stages;
   const uint32_t qk_layout = swizzle_layout_code(p.qk_row_bytes);
   const bool fp8 = p.qk_is_fp8 != 0;
@@ -274,58 +408,94 @@ __device__ void qk_issuer_role(const Ctx& c) {
   const uint32_t md_lo = (uint32_t)md0, md_hi = (uint32_t)(md0 >> 32);
   const uint32_t idesc_mask = make_idesc(1u, 1u, 0u, 0u, kTile);
   const bool mask_col = p.mask_col != 0;
+  // bias slices: A = 16 keys of the staged bias tile (K-major, 128-byte swizzled rows, two boxes
+  // of 64 keys), B = the 16 x 16 identity (K-major, no swizzle: 8-key halves 256 bytes apart,
+  // 8-row groups 128 bytes apart), D = 16 columns of the logits tile
+  const uint64_t bd0 = make_smem_desc(c.smem + p.off_bias, 16, 8 * 128, 2);
+  const uint64_t id0 = make_smem_desc(c.smem + p.off_ident, 256, 128, 0);
+  const uint32_t bd_lo = (uint32_t)bd0, bd_hi = (uint32_t)(bd0 >> 32);
+  const uint32_t id_lo = (uint32_t)id0, id_hi = (uint32_t)(id0 >> 32);
+  const uint32_t idesc_bias = make_idesc(1u, 1u, 0u, 0u, 16);
   long long* tl = (p.debug != nullptr && blockIdx.x == 0)
                       ? reinterpret_cast<long long*>(p.debug + kDbgFloats) + 2 * kDbgTimelineTiles * 8
                       : nullptr;
   uint32_t tl_n = 0;
-  // ring positions / barrier parities are carried incrementally: no division on this thread
-  uint32_t st = 0, kv_par = 0, icount = 0;
+  // ring positions / barrier parities are carried incrementally: no division on this warp
+  uint32_t st = 0, kv_par = 0, icount = 0, bst = 0, b_par = 0;
   uint32_t sfree_par[2] = {0, 0}, first[2] = {1, 1};
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
     const Item it = decode_item(p, item);
     const int gv = it.gv;
-    AF3K_WAIT(c, BarIdx::q_full, icount & 1);
     for (int kt = 0; kt < p.n_kt; ++kt) {
+      if (kTcBias) AF3K_WAIT_WARP(c, BarIdx::bias_full + bst, b_par);
       for (int s = 0; s < gv; ++s) {
         const int b = s & 1;
         // the softmax warpgroup of this buffer must have read the previous logits tile
         if (b) {
-          if (!first[1]) { AF3K_WAIT(c, BarIdx::s_free + 1, sfree_par[1]); sfree_par[1] ^= 1; }
+          if (!first[1]) { AF3K_WAIT_WARP(c, BarIdx::s_free + 1, sfree_par[1]); sfree_par[1] ^= 1; }
           first[1] = 0;
         } else {
-          if (!first[0]) { AF3K_WAIT(c, BarIdx::s_free + 0, sfree_par[0]); sfree_par[0] ^= 1; }
+          if (!first[0]) { AF3K_WAIT_WARP(c, BarIdx::s_free + 0, sfree_par[0]); sfree_par[0] ^= 1; }
           first[0] = 0;
         }
-        AF3K_WAIT(c, BarIdx::kv_full + st, kv_par);
-        const long long t0 = tl != nullptr ? clock64() : 0;
+        const int qslot = (int)(icount & 1) * kMaxStreams + s;   // Q tiles are double-buffered by item
+        if (kt == 0) AF3K_WAIT_WARP(c, (kTcBias ? BarIdx::q_scaled : BarIdx::q_full) + qslot, (icount >> 1) & 1);
+        AF3K_WAIT_WARP(c, BarIdx::kv_full + st, kv_par);
         tc_fence_after();
-        const uint32_t a_lo = qd_lo + s * q_step;
+        const uint32_t a_lo = qd_lo + ((icount & 1) * p.G + s) * q_step;
         const uint32_t b_lo = kd_lo + st * stage_step;
         const uint32_t s_tmem = c.tmem + kSCol + b * kTile;
+        const uint32_t slot16 = st * (kMaskPanelBytes >> 4);
+        const uint32_t bias_lo = bd_lo + bst * (kBiasTileBytes >> 4);
+        if (leader) {
+          const long long t0 = tl != nullptr ? clock64() : 0;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {     // one K step = 32 bytes of a tile row
-          if (k < ksteps) {
-            if (fp8) mma_ss_f8(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
-            else     mma_ss_f16(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) {     // one K step = 32 bytes of a tile row
+            if (k < ksteps) {
+              if (fp8) mma_ss_f8(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
+              else     mma_ss_f16(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
+            }
           }
+          // mask column: start address and leading offset both move with the ring slot (the
+          // zero block stays put)
+          if (mask_col)
+            mma_ss_f16(s_tmem, od_lo, od_hi, md_lo + slot16 - (slot16 << 16), md_hi, idesc_mask, 1u);
+          if (kTcBias) {
+#pragma unroll
+            for (int k = 0; k < kTile / 16; ++k)   // keys 16k .. 16k + 15: box k / 4, 32 bytes per step
+              mma_ss_f16(s_tmem + 16 * k, bias_lo + (k >> 2) * (kBiasTileBytes >> 5) + 2 * (k & 3), bd_hi,
+                         id_lo, id_hi, idesc_bias, 1u);
+          }
+          tc_commit(bar_addr(c, BarIdx::s_full + b));
+          if (kt == p.n_kt - 1) tc_commit(bar_addr(c, BarIdx::q_empty + qslot));
+          if (tl != nullptr && tl_n + 2 <= 2 * kDbgTimelineTiles) { tl[tl_n++] = t0; tl[tl_n++] = clock64(); }
         }
-        if (mask_col) {
-          // start address and leading offset both move with the ring slot: the zero block stays put
-          const uint32_t slot16 = st * (kMaskPanelBytes >> 4);
-          mma_ss_f16(s_tmem, od_lo, od_hi, md_lo + slot16 - (slot16 << 16), md_hi, idesc_mask, 1u);
-        }
-        tc_commit(bar_addr(c, BarIdx::s_full + b));
-        if (kt == p.n_kt - 1 && s == gv - 1) tc_commit(bar_addr(c, BarIdx::q_empty));
-        if (tl != nullptr && tl_n + 2 <= 2 * kDbgTimelineTiles) { tl[tl_n++] = t0; tl[tl_n++] = clock64(); }
+        __syncwarp();
         if (++st == nkv) { st = 0; kv_par ^= 1; }
+      }
+      if (kTcBias) {
+        // every stream's bias MMAs of this key tile are issued: the bias stage is free when they finish
+        if (leader) tc_commit(bar_addr(c, BarIdx::bias_empty + bst));
+        __syncwarp();
+        if (++bst == kBiasStages) { bst = 0; b_par ^= 1; }
       }
     }
   }
 }
 
-// O += P V for every tile, in order.
-__device__ void pv_issuer_role(const Ctx& c) {
+// O += P V for every tile, in order.  This warp mostly waits for the softmax warpgroups, so (bf16
+// q/k) it also scales the Q tiles: the first item's up front, the next item's in 1 KB pieces
+// while it waits, what is left when the item's last P V has been issued.
+template <bool kTcBias>
+__device__ void pv_issuer_role(const Ctx& c, int lane) {
   const AttnParams& p = *c.p;
+  const bool leader = elect_one();
+  QScaler scaler;
+  if (kTcBias && (int)blockIdx.x < p.n_items) {
+    scaler.start(0, decode_item(p, blockIdx.x).gv);
+    while (scaler.pending())
+      if (scaler.step(c, lane, true) < 0) return;
+  }
   const uint32_t nkv = p.kv_stages;
   const uint32_t v_layout = swizzle_layout_code(p.v_row_bytes);
   const uint32_t idesc_pv = make_idesc(1u, 1u, 0u, 1u, (uint32_t)p.nv);
@@ -345,30 +515,35 @@ __device__ void pv_issuer_role(const Ctx& c) {
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
     const Item it = decode_item(p, item);
     const int gv = it.gv;
+    scaler.start(icount + 1, (kTcBias && item + (int)gridDim.x < p.n_items) ? decode_item(p, item + gridDim.x).gv : 0);
     for (int kt = 0; kt < p.n_kt; ++kt) {
       for (int s = 0; s < gv; ++s) {
         const int b = s & 1;
-        if (b) { AF3K_WAIT(c, BarIdx::p_ready + 1, pready_par[1]); pready_par[1] ^= 1; }
-        else   { AF3K_WAIT(c, BarIdx::p_ready + 0, pready_par[0]); pready_par[0] ^= 1; }
-        // the previous item's epilogue must have read every O accumulator before the first
-        // P V of this item overwrites one
-        if (kt == 0 && s == 0 && icount > 0) AF3K_WAIT(c, BarIdx::epi_done, (icount - 1) & 1);
-        const long long t0 = tl != nullptr ? clock64() : 0;
+        if (b) { AF3K_WAIT_WARP_OR_SCALE(c, BarIdx::p_ready + 1, pready_par[1], scaler, lane); pready_par[1] ^= 1; }
+        else   { AF3K_WAIT_WARP_OR_SCALE(c, BarIdx::p_ready + 0, pready_par[0], scaler, lane); pready_par[0] ^= 1; }
+        // the warpgroup's epilogue of the previous item must have read its O accumulators before
+        // its first P V of this item overwrites one
+        if (kt == 0 && s < 2 && icount > 0) AF3K_WAIT_WARP(c, BarIdx::epi_done + b, (icount - 1) & 1);
         tc_fence_after();
         const uint32_t b_lo = vd_lo + st * stage_step;
         const uint32_t o_tmem = c.tmem + kOCol + s * p.nv;
         const uint32_t p_tmem = c.tmem + kPCol + b * 64;
-        mma_ts_f16(o_tmem, p_tmem, b_lo, vd_hi, idesc_pv, kt > 0 ? 1u : 0u);
+        if (leader) {
+          const long long t0 = tl != nullptr ? clock64() : 0;
+          mma_ts_f16(o_tmem, p_tmem, b_lo, vd_hi, idesc_pv, kt > 0 ? 1u : 0u);
 #pragma unroll
-        for (int k = 1; k < kTile / 16; ++k)   // 16 keys per step: 8 TMEM columns of P
-          mma_ts_f16(o_tmem, p_tmem + k * 8, b_lo + k * v_kstep, vd_hi, idesc_pv, 1u);
-        // one completion signal: the K/V stage is free, and so are this tile's P buffer and O
-        tc_commit(bar_addr(c, BarIdx::kv_empty + st));
-        if (tl != nullptr && tl_n + 2 <= 2 * kDbgTimelineTiles) { tl[tl_n++] = t0; tl[tl_n++] = clock64(); }
+          for (int k = 1; k < kTile / 16; ++k)   // 16 keys per step: 8 TMEM columns of P
+            mma_ts_f16(o_tmem, p_tmem + k * 8, b_lo + k * v_kstep, vd_hi, idesc_pv, 1u);
+          // one completion signal: the K/V stage is free, and so are this tile's P buffer and O
+          tc_commit(bar_addr(c, BarIdx::kv_empty + st));
+          if (tl != nullptr && tl_n + 2 <= 2 * kDbgTimelineTiles) { tl[tl_n++] = t0; tl[tl_n++] = clock64(); }
+        }
+        __syncwarp();
         if (++st == nkv) st = 0;
       }
     }
-    tc_commit(bar_addr(c, BarIdx::item_done));
+    while (scaler.pending())
+      if (scaler.step(c, lane, true) < 0) return;
   }
 }
 
@@ -408,9 +583,21 @@ __device__ __forceinline__ void logits_half(uint32_t (&xr)[kTile], uint32_t bias
   }
 }
 
+// Row maximum over 64 finished logits (bf16 q/k: the tensor core has already applied scale, bias
+// and mask).
+template <int kCol0>
+__device__ __forceinline__ void max_half(const uint32_t (&xr)[kTile], float& mxa, float& mxb) {
+#pragma unroll
+  for (int i = kCol0; i < kCol0 + 64; i += 4) {
+    mxa = max3(mxa, __uint_as_float(xr[i]), __uint_as_float(xr[i + 1]));
+    mxb = max3(mxb, __uint_as_float(xr[i + 2]), __uint_as_float(xr[i + 3]));
+  }
+}
+
 // One 128 x 128 logits tile of one stream; the thread owns row `row` (TMEM lane).
 // m_run is the reference maximum the running sums are scaled by (it may lag the true maximum by
 // up to kLazyRescaleLog2 bits), l_run the running sum of the fp32 weights.
+template <bool kTcBias>
 __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, int lane,
                                              uint32_t s_taddr, uint32_t p_taddr, uint32_t o_taddr,
                                              int nv, uint32_t bias_row, uint32_t row7, float scale,
@@ -429,7 +616,8 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
   }
   const uint64_t scale2 = pack_f32x2(scale, scale);
   float mxa = -INFINITY, mxb = -INFINITY;
-  logits_half<0>(xr, bias_row, row7, scale2, mxa, mxb);
+  if (kTcBias) max_half<0>(xr, mxa, mxb);
+  else         logits_half<0>(xr, bias_row, row7, scale2, mxa, mxb);
   tc_wait_ld();
   // the logits are in registers: hand the S buffer back so that the next Q K^T can start
   tc_fence_before();
@@ -439,7 +627,8 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
 #pragma unroll
     for (int i = 64; i < kTile; ++i) dbg[kDbgS + i] = __uint_as_float(xr[i]);
   }
-  logits_half<64>(xr, bias_row, row7, scale2, mxa, mxb);
+  if (kTcBias) max_half<64>(xr, mxa, mxb);
+  else         logits_half<64>(xr, bias_row, row7, scale2, mxa, mxb);
 
   const float mt = fmaxf(mxa, mxb);
   if (ts != nullptr) ts[2] = clock64() + (long long)(mt == 123.456f);   // after the logits pass
@@ -455,58 +644,71 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
       alpha = ex2_approx((m_run - mt) * kLog2e);
     }
   }
-  // P buffer and O accumulator are free once the previous P V of this warpgroup has finished:
-  // that is the completion that also frees the previous tile's K/V stage
-  if (wait_prev_pv) {
-    const bool ok = mbar_wait_bounded(bar_addr(c, prev_pv_bar), prev_pv_parity, c.p->wait_limit,
-                                      c.abort_flag);
-    if (!__all_sync(0xffffffffu, ok)) {
-      report_timeout(c, prev_pv_bar);
-      return false;
-    }
-    tc_fence_after();
-  }
-  if (__any_sync(0xffffffffu, need)) {
-    for (int c0 = 0; c0 < nv; c0 += 16) {
-      uint32_t o[16];
-      tmem_ld_x16(o_taddr + c0, o);
-      tc_wait_ld();
-#pragma unroll
-      for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-      tmem_st_x16(o_taddr + c0, o);
-    }
-  }
-
-  if (ts != nullptr) ts[3] = clock64();   // P buffer free, O rescaled
-  // p = exp2((x - m) * log2e).  The subtraction comes first so that x == m gives exactly 0 even
-  // for the huge negative values of masked keys (a row with no attended key: all weights 1).
+  if (ts != nullptr) ts[3] = clock64();   // row maximum known
+  // p = exp2((x - m) * log2e).  fp8 path: the subtraction comes first so that x == m gives
+  // exactly 0 even for the huge negative values of masked keys (a row with no attended key: all
+  // weights 1).  bf16 path: one fused multiply-add, x * log2e - m * log2e; for such a row x and
+  // m are the same power of two, both products are exact and the result is 0 as well.
   const uint64_t l2e2 = pack_f32x2(kLog2e, kLog2e);
   const uint64_t nm2 = pack_f32x2(-m_use, -m_use);
+  const float nml = -m_use * kLog2e;
+  const uint64_t nml2 = pack_f32x2(nml, nml);
   uint64_t suma = pack_f32x2(0.f, 0.f), sumb = suma;
+  // The first kHeld column groups are computed before anything is written: the P buffer and the
+  // O accumulator only become free when the previous P V of this warpgroup has finished, and that
+  // wait is taken as late as the registers allow.
+  constexpr int kHeld = 3;
+  uint32_t pk[8][8];
 #pragma unroll
   for (int cidx = 0; cidx < 8; ++cidx) {
-    uint32_t pk[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int col = cidx * 16 + 2 * i;
       float y0, y1;
-      const uint64_t d2 = add_f32x2(pack_f32x2(__uint_as_float(xr[col]), __uint_as_float(xr[col + 1])), nm2);
-      unpack_f32x2(mul_f32x2(d2, l2e2), y0, y1);
+      const uint64_t x2 = pack_f32x2(__uint_as_float(xr[col]), __uint_as_float(xr[col + 1]));
+      if (kTcBias) unpack_f32x2(fma_f32x2(x2, l2e2, nml2), y0, y1);
+      else         unpack_f32x2(mul_f32x2(add_f32x2(x2, nm2), l2e2), y0, y1);
       const float p0 = ex2_approx(y0);
       const float p1 = ex2_approx(y1);
       if (i & 1) sumb = add_f32x2(sumb, pack_f32x2(p0, p1));
       else       suma = add_f32x2(suma, pack_f32x2(p0, p1));
-      pk[i] = pack_bf16x2(p0, p1);
+      pk[cidx][i] = pack_bf16x2(p0, p1);
     }
     if (dbg != nullptr) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dbg[kDbgP + cidx * 8 + i] = __uint_as_float(pk[i]);
+      for (int i = 0; i < 8; ++i) dbg[kDbgP + cidx * 8 + i] = __uint_as_float(pk[cidx][i]);
     }
-    // P as bf16, two keys per 32-bit TMEM column: the A operand of the second GEMM
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
-                 ::"r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
-                 "r"(pk[6]), "r"(pk[7]), "r"(p_taddr + cidx * 8)
-                 : "memory");
+    if (cidx == kHeld - 1) {
+      // the completion that frees P and O is the one that also frees the previous tile's K/V stage
+      if (wait_prev_pv) {
+        const bool ok = mbar_wait_bounded(bar_addr(c, prev_pv_bar), prev_pv_parity, c.p->wait_limit,
+                                          c.abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) {
+          report_timeout(c, prev_pv_bar);
+          return false;
+        }
+        tc_fence_after();
+      }
+      if (__any_sync(0xffffffffu, need)) {
+        for (int c0 = 0; c0 < nv; c0 += 16) {
+          uint32_t o[16];
+          tmem_ld_x16(o_taddr + c0, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_x16(o_taddr + c0, o);
+        }
+      }
+    }
+    if (cidx >= kHeld - 1) {
+      // P as bf16, two keys per 32-bit TMEM column: the A operand of the second GEMM
+#pragma unroll
+      for (int cc = (cidx == kHeld - 1 ? 0 : cidx); cc <= cidx; ++cc)
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
+                     ::"r"(pk[cc][0]), "r"(pk[cc][1]), "r"(pk[cc][2]), "r"(pk[cc][3]), "r"(pk[cc][4]),
+                     "r"(pk[cc][5]), "r"(pk[cc][6]), "r"(pk[cc][7]), "r"(p_taddr + cc * 8)
+                     : "memory");
+    }
   }
   tc_wait_st();
   if (ts != nullptr) ts[4] = clock64();   // P stored
@@ -518,7 +720,7 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
   return true;
 }
 
-template <bool kDebug>
+template <bool kDebug, bool kTcBias>
 __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
   const AttnParams& p = *c.p;
   const int row = wq * 32 + lane;                    // row of the 128-query tile == TMEM lane
@@ -538,9 +740,11 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
     float scale = p.scale;
     if (p.q_scale != nullptr) scale *= p.q_scale[it.h] * p.k_scale[it.h];
 
+    long long* last_ts = nullptr;     // debug build: timeline slot of the warpgroup's last tile
     for (int kt = 0; kt < p.n_kt; ++kt) {
+      // fp8 q/k: this thread adds the bias itself, from its row of the staged tile
       const uint32_t bst = bcount % kBiasStages;
-      AF3K_WAIT_WARP(c, BarIdx::bias_full + bst, (bcount / kBiasStages) & 1);
+      if (!kTcBias) AF3K_WAIT_WARP(c, BarIdx::bias_full + bst, (bcount / kBiasStages) & 1);
       const uint32_t bias_row = c.smem + p.off_bias + bst * kBiasTileBytes + row * 128;
 
       for (int s = wg; s < it.gv; s += 2) {
@@ -553,6 +757,7 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
         if (kDebug && p.debug != nullptr && blockIdx.x == 0 && wq == 0 && lane == 0 && ucnt < kDbgTimelineTiles)
           ts = reinterpret_cast<long long*>(p.debug + kDbgFloats) + ((size_t)wg * kDbgTimelineTiles + ucnt) * 8;
         if (ts != nullptr) ts[0] = clock64();
+        if (kDebug) last_ts = ts;
         AF3K_WAIT_WARP(c, BarIdx::s_full + wg, ucnt & 1);
         tc_fence_after();
         if (ts != nullptr) ts[1] = clock64();
@@ -560,7 +765,7 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
         float* dbg = nullptr;
         if (kDebug && p.debug != nullptr && blockIdx.x == 0 && icount == 0 && s == 0 && kt == 0)
           dbg = p.debug + (size_t)row * kTile;
-        if (!softmax_tile(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row, row & 7, scale,
+        if (!softmax_tile<kTcBias>(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row, row & 7, scale,
                           kt == 0, ucnt > 0, BarIdx::kv_empty + (int)prev_stage, prev_round & 1, m_run,
                           l_run, ts))
           return;
@@ -576,19 +781,24 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
         st_m[s * kTile + row] = m_run;
         st_l[s * kTile + row] = l_run;
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::bias_empty + bst));
+      if (!kTcBias) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::bias_empty + bst));
+      }
       ++bcount;
     }
 
     g_item += (uint32_t)(p.n_kt * it.gv);
 
-    // ---- epilogue: O / l -> bf16 -> global
-    AF3K_WAIT_WARP(c, BarIdx::item_done, icount & 1);
+    // ---- epilogue: O / l -> bf16 -> global, once this warpgroup's last P V has finished (the
+    // other warpgroup may still be working on its own streams)
+    if (kDebug && last_ts != nullptr) last_ts[5] = clock64();
+    if (ucnt > 0) AF3K_WAIT_WARP(c, BarIdx::kv_empty + (int)prev_stage, prev_round & 1);
     tc_fence_after();
+    if (kDebug && last_ts != nullptr) last_ts[6] = clock64();
     const int qrow = it.qt * kTile + row;
     for (int s = wg; s < it.gv; s += 2) {
-      const float inv = 1.0f / st_l[s * kTile + row];
+      const float inv = __frcp_rn(st_l[s * kTile + row]);
       const uint32_t o_taddr = c.tmem + lane_sel + kOCol + s * p.nv;
       __nv_bfloat16* orow = p.out + (long long)(it.r0 + s) * p.out_stride_b1 +
                             (long long)it.h * p.out_stride_b2 + (long long)qrow * p.out_stride_s;
@@ -620,12 +830,13 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
     }
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::epi_done));
+    if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::epi_done + wg));
+    if (kDebug && last_ts != nullptr) last_ts[7] = clock64();
   }
 }
 
 // ------------------------------------------------------------------ kernel
-template <bool kDebug>
+template <bool kDebug, bool kTcBias>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -649,18 +860,21 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
     prefetch_tensormap(&tm_k);
     prefetch_tensormap(&tm_v);
     prefetch_tensormap(&tm_bias);
-    mbar_init(bar_addr(c, BarIdx::q_full), 1);
-    mbar_init(bar_addr(c, BarIdx::q_empty), 1);
-    mbar_init(bar_addr(c, BarIdx::item_done), 1);
-    mbar_init(bar_addr(c, BarIdx::epi_done), 8);
+    for (int i = 0; i < 2 * kMaxStreams; ++i) {
+      mbar_init(bar_addr(c, BarIdx::q_full + i), 1);
+      mbar_init(bar_addr(c, BarIdx::q_empty + i), 1);
+      mbar_init(bar_addr(c, BarIdx::q_scaled + i), 1);
+    }
     for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_addr(c, BarIdx::epi_done + i), 4);
       mbar_init(bar_addr(c, BarIdx::s_full + i), 1);
       mbar_init(bar_addr(c, BarIdx::s_free + i), 4);
       mbar_init(bar_addr(c, BarIdx::p_ready + i), 4);
     }
     for (int i = 0; i < kBiasStages; ++i) {
       mbar_init(bar_addr(c, BarIdx::bias_full + i), 1);
-      mbar_init(bar_addr(c, BarIdx::bias_empty + i), 8);
+      // freed by the bias MMAs' completion (bf16 q/k) or by the eight softmax warps (fp8 q/k)
+      mbar_init(bar_addr(c, BarIdx::bias_empty + i), kTcBias ? 1 : 8);
     }
     for (int i = 0; i < kMaxKvStages; ++i) {
       mbar_init(bar_addr(c, BarIdx::kv_full + i), p.mask_col ? 2 : 1);
@@ -672,16 +886,21 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
     tmem_alloc(smem_u32(&tmem_base_slot), kTmemCols);
     tmem_relinquish();
   }
-  if (warp == 3 && p.mask_col) {
-    // ones column, mask-column ring and zero block are contiguous: clear them, then set
-    // element (row, 0) of the ones operand to bf16 1.0
+  if (warp == 3) {
+    // ones column, mask-column ring, zero block and identity are contiguous: clear them, then set
+    // element (row, 0) of the ones operand and the identity's diagonal to bf16 1.0
     const uint32_t base = c.smem + p.off_ones;
-    const uint32_t bytes = p.off_zero + kMaskPanelBytes - p.off_ones;
+    const uint32_t bytes = p.off_ident + kIdentBytes - p.off_ones;
     for (uint32_t o = lane * 16; o < bytes; o += 32 * 16)
       asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(base + o), "r"(0u) : "memory");
     __syncwarp();
     for (int r = lane; r < kTile; r += 32)
       asm volatile("st.shared.u16 [%0], %1;" ::"r"(base + r * 16), "h"((uint16_t)0x3F80) : "memory");
+    // identity element (i, i): 8-row group i / 8 (128 bytes apart), 8-key half i / 8 (256 bytes
+    // apart), row i % 8 (16 bytes), key i % 8 (2 bytes)
+    if (lane < 16)
+      asm volatile("st.shared.u16 [%0], %1;" ::"r"(c.smem + p.off_ident + (lane >> 3) * 384 + (lane & 7) * 18),
+                   "h"((uint16_t)0x3F80) : "memory");
     fence_proxy_async_smem();
   }
   tc_fence_before();
@@ -695,15 +914,15 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
     if (warp == 0) {
       if (lane == 0) producer_role(c, &tm_q, &tm_k, &tm_v, &tm_bias);
     } else if (warp == 1) {
-      if (lane == 0) qk_issuer_role(c);
+      qk_issuer_role<kTcBias>(c);
     } else if (warp == 2) {
-      if (lane == 0) pv_issuer_role(c);
+      pv_issuer_role<kTcBias>(c, lane);
     } else if (warp == 3) {
       if (p.mask_col) mask_writer_role(c, lane);
     }
   } else {
     setmaxnreg_inc<kRegsSoftmax>();
-    softmax_role<kDebug>(c, (warp - 4) >> 2, warp & 3, lane);
+    softmax_role<kDebug, kTcBias>(c, (warp - 4) >> 2, warp & 3, lane);
   }
 
   tc_fence_before();

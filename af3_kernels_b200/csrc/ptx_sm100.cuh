@@ -76,10 +76,13 @@ __device__ __forceinline__ bool mbar_try_wait_park(uint32_t bar, uint32_t parity
 
 // Bounded wait: returns false when `limit_cycles` SM clocks passed without the
 // phase completing, or when another thread of the CTA already raised *abort_flag.
+// A phase that is already complete is detected with test_wait (about half the cost of a
+// try_wait that passes); the waiting loop parks the thread so that it leaves the issue slots
+// to the warps that are working.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   long long limit_cycles,
                                                   volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_test_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
@@ -89,6 +92,19 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
       if (clock64() - t0 > limit_cycles) return false;
     }
   }
+}
+
+// One lane of a converged warp (the same lane every time it is asked within a kernel run).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 // ---------------------------------------------------------------- TMA loads
@@ -144,9 +160,8 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                    bar)
                : "memory");
 }
-// The issuing thread is a single lane, so every instruction on its path costs a full dependent
-// issue.  Descriptors are therefore passed as {low word, high word}: only the low word (start
-// address) changes from one MMA to the next and it advances by a plain 32-bit add.
+// Descriptors are passed as {low word, high word}: only the low word (start address) changes
+// from one MMA to the next and it advances by a plain 32-bit add.
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void mma_ss_f16(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
                                            uint32_t b_lo, uint32_t b_hi, uint32_t idesc,

@@ -277,8 +277,9 @@ def test_launch_count(cuda_device):
 
 
 def test_debug_dump_shows_the_tensor_core_stages(cuda_device):
-    """The diagnostic build dumps the first logits tile: raw Q K^T (+ mask column), P as written to
-    TMEM, the un-normalised accumulator and the row statistics.  Checking each against plain fp32
+    """The diagnostic build dumps the first logits tile: the logits as the tensor core delivers them
+    (scaled Q K^T + bias + mask column), P as written to TMEM, the un-normalised accumulator and
+    the row statistics.  Checking each against plain fp32
     math pins the operand layouts (swizzled K-major Q/K, MN-major V, P in TMEM, mask column)."""
     dev = cuda_device
     lib = _capi.load()
@@ -298,10 +299,14 @@ def test_debug_dump_shows_the_tensor_core_stages(cuda_device):
     finally:
         lib.af3k_debug_set_dump(None)
     d = dump[: 4 * 128 * 128].view(4, 128, 128).cpu()
-    s_ref = q[0, 0].float().cpu() @ k[0, 0].float().cpu().T
+    # with bf16 q/k the tensor core delivers the finished logit: q is scaled and rounded to bf16 in
+    # shared memory first (the reference's own first step), the bias is added by identity MMAs
+    q_scaled = (q[0, 0].float().cpu() * D ** -0.5).to(torch.bfloat16).float()
+    x_ref = q_scaled @ k[0, 0].float().cpu().T + bias[0].float().cpu()
     keep = mask[None, :].expand(S, S)
-    assert (d[0][keep] - s_ref[keep]).abs().max().item() <= 1e-4          # attended keys: q . k
+    assert (d[0][keep] - x_ref[keep]).abs().max().item() <= 1e-4          # attended keys
     assert (d[0][~keep] == -(2.0 ** 47)).all()                             # masked keys: exactly -2^47
+    s_ref = q[0, 0].float().cpu() @ k[0, 0].float().cpu().T
     p_words = d[1][:, :64].contiguous().view(torch.int32)
     p_lo = (p_words << 16).view(torch.float32)
     p_hi = (p_words & -65536).view(torch.float32)
