@@ -165,7 +165,7 @@ int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
 
   const int budget = dev.max_smem_optin - 1024 /*alignment slack*/ - kStaticSmemReserve;
   p.mask_col = 1;   // set for real in the launch path once the mask pointer is known
-  const int fixed = kBiasStages * kBiasTileBytes + kMaxStreams * kTile * 8 + (int)kBarrierBlockBytes +
+  const int fixed = kBiasStages * kBiasTileBytes + (int)kBarrierBlockBytes +
                     (kMaxKvStages + 2) * (int)kMaskPanelBytes /*ones column, mask ring, zero block*/ +
                     (int)kIdentBytes;
   const int kv_stage = (int)(p.k_tile_bytes + p.v_tile_bytes);
@@ -208,7 +208,6 @@ int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
   p.off_q = off;      off += 2 * p.G * p.q_tile_bytes;
   p.off_kv = off;     off += p.kv_stages * kv_stage;
   p.off_bias = off;   off += kBiasStages * kBiasTileBytes;
-  p.off_state = off;  off += kMaxStreams * kTile * 8;
   p.off_bar = off;    off += kBarrierBlockBytes;
   p.off_ones = off;   off += kMaskPanelBytes;
   p.off_mcol = off;   off += kMaxKvStages * kMaskPanelBytes;

@@ -98,7 +98,7 @@ struct AttnParams {
   long long wait_limit;  // SM clocks a single wait may take before the kernel gives up
   float* debug;          // diagnostic dump of block 0's first logits tile (debug build of the kernel)
   uint32_t q_tile_bytes, k_tile_bytes, v_tile_bytes;
-  uint32_t off_q, off_kv, off_bias, off_state, off_bar;   // from the 1024-aligned smem base
+  uint32_t off_q, off_kv, off_bias, off_bar;   // from the 1024-aligned smem base
   // mask-column operands of the extra K step (all no-swizzle, K-major, 16-byte rows):
   //   off_ones: A operand, element (row, 0) = 1;  off_mcol: ring of per-tile B operands, element
   //   (key, 0) = mask value;  off_zero: the all-zero second half of K shared by both.
@@ -649,6 +649,10 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
   // exactly 0 even for the huge negative values of masked keys (a row with no attended key: all
   // weights 1).  bf16 path: one fused multiply-add, x * log2e - m * log2e; for such a row x and
   // m are the same power of two, both products are exact and the result is 0 as well.
+  // What bounds this pass: a scheduler issues an ex2 over 8 cycles and no FMA-pipe instruction of
+  // any of its warps overlaps with that (measured), so a tile costs 128 x 8 cycles plus its
+  // FMA-pipe instructions, while ALU-pipe work (the maximum, the bf16 packing) is free.  The
+  // packed f32x2 forms halve the FMA-pipe instruction count at the same cost per value.
   const uint64_t l2e2 = pack_f32x2(kLog2e, kLog2e);
   const uint64_t nm2 = pack_f32x2(-m_use, -m_use);
   const float nml = -m_use * kLog2e;
@@ -727,12 +731,12 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
   const uint32_t lane_sel = (uint32_t)(wq * 32) << 16;
   const uint32_t s_taddr = c.tmem + lane_sel + kSCol + wg * kTile;
   const uint32_t p_taddr = c.tmem + lane_sel + kPCol + wg * 64;
-  float* st_m = reinterpret_cast<float*>(__cvta_shared_to_generic(c.smem + p.off_state));
-  float* st_l = st_m + kMaxStreams * kTile;
+  // running statistics of the warpgroup's (at most two) streams, kept in registers
+  float m_st[2] = {-INFINITY, -INFINITY}, l_st[2] = {0.f, 0.f};
   uint32_t ucnt = 0, bcount = 0, icount = 0;         // tiles done by this warpgroup, bias tiles, items
   // position of tiles in the CTA-wide order (all streams): gives the K/V stage a tile used
-  uint32_t g_item = 0;                                // tiles of all earlier items
-  uint32_t prev_stage = 0, prev_round = 0;            // stage / ring round of this warpgroup's last tile
+  uint32_t kt_stage = 0, kt_round = 0;                // ring stage / lap of stream 0's tile at the current key tile
+  uint32_t prev_stage = 0, prev_round = 0;            // the same for this warpgroup's last tile
   const uint32_t nkv = p.kv_stages;
 
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
@@ -749,7 +753,8 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
 
       for (int s = wg; s < it.gv; s += 2) {
         float m_run = -INFINITY, l_run = 0.f;
-        if (kt > 0) { m_run = st_m[s * kTile + row]; l_run = st_l[s * kTile + row]; }
+        const int si = (s - wg) >> 1;
+        if (kt > 0) { m_run = si ? m_st[1] : m_st[0]; l_run = si ? l_st[1] : l_st[0]; }
 
         // diagnostic timeline (debug build only): SM clock at the phase boundaries of every tile
         // this warp processes, 8 slots per tile, behind the tile dump
@@ -771,24 +776,25 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
           return;
         ++ucnt;
         {
-          const uint32_t g = g_item + (uint32_t)(kt * it.gv + s);
-          prev_stage = g % nkv;
-          prev_round = g / nkv;
+          // tiles are numbered in the producer's order; the numbers are carried without a division
+          prev_stage = kt_stage + (uint32_t)s;
+          prev_round = kt_round;
+          while (prev_stage >= nkv) { prev_stage -= nkv; ++prev_round; }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::p_ready + wg));
-        st_m[s * kTile + row] = m_run;
-        st_l[s * kTile + row] = l_run;
+        if (si) { m_st[1] = m_run; l_st[1] = l_run; } else { m_st[0] = m_run; l_st[0] = l_run; }
       }
       if (!kTcBias) {
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::bias_empty + bst));
       }
       ++bcount;
+      kt_stage += (uint32_t)it.gv;
+      while (kt_stage >= nkv) { kt_stage -= nkv; ++kt_round; }
     }
 
-    g_item += (uint32_t)(p.n_kt * it.gv);
 
     // ---- epilogue: O / l -> bf16 -> global, once this warpgroup's last P V has finished (the
     // other warpgroup may still be working on its own streams)
@@ -798,7 +804,7 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
     if (kDebug && last_ts != nullptr) last_ts[6] = clock64();
     const int qrow = it.qt * kTile + row;
     for (int s = wg; s < it.gv; s += 2) {
-      const float inv = __frcp_rn(st_l[s * kTile + row]);
+      const float inv = __frcp_rn(s == wg ? l_st[0] : l_st[1]);
       const uint32_t o_taddr = c.tmem + lane_sel + kOCol + s * p.nv;
       __nv_bfloat16* orow = p.out + (long long)(it.r0 + s) * p.out_stride_b1 +
                             (long long)it.h * p.out_stride_b2 + (long long)qrow * p.out_stride_s;
@@ -810,8 +816,8 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
           float* dbg = p.debug + (size_t)row * kTile;
 #pragma unroll
           for (int i = 0; i < 16; ++i) dbg[kDbgO + c0 + i] = __uint_as_float(o[i]);
-          dbg[kDbgML + 0] = st_m[s * kTile + row];
-          dbg[kDbgML + 1] = st_l[s * kTile + row];
+          dbg[kDbgML + 0] = m_st[0];
+          dbg[kDbgML + 1] = l_st[0];
         }
         if (qrow < p.Sq) {
 #pragma unroll
