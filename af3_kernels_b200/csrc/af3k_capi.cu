@@ -173,39 +173,44 @@ int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
   int g_max = kMaxStreams < g_tmem ? kMaxStreams : g_tmem;
   if (g_max > p.B1) g_max = p.B1 > 0 ? p.B1 : 1;
 
-  int best_g = 0, best_stages = 0;
+  int best_g = 0, best_stages = 0, best_qbuf = 0;
   double best_cost = 0;
   // rows_per_item is a request: it is honoured up to what TMEM and the batch allow
   const int g_req = d.rows_per_item > g_max ? g_max : d.rows_per_item;
   for (int g = 1; g <= g_max; ++g) {
     if (g_req != 0 && g != g_req) continue;
-    int stages = (budget - fixed - 2 * g * (int)p.q_tile_bytes) / kv_stage;   // Q tiles are double-buffered
-    if (stages > kMaxKvStages) stages = kMaxKvStages;
-    if (stages < 2) continue;
-    const long long groups = (p.B1 + g - 1) / g;
-    const long long items = groups * p.B2 * p.n_qt;
-    const long long rounds = (items + dev.sm_count - 1) / dev.sm_count;
-    // streams alternate between the two softmax warpgroups: an odd count leaves one idle slot.
-    // A CTA's time, in logits-tile times of one warpgroup: per item n_kt tiles for each of its
-    // slots / 2 streams plus about 0.8 for the epilogue and the hand-over to the next item.
-    const int slots = (g & 1) ? g + 1 : g;
-    double cost = (double)rounds * (p.n_kt * (slots / 2) + 0.8);
-    // a K/V tile takes about two thousand cycles to arrive, most of a logits tile's time: with a
-    // short ring the MMAs wait for their operands (measured: 4 stages cost about 3 %)
-    static const double kRingPenalty[7] = {0, 0, 1.4, 1.15, 1.03, 1.0, 1.0};
-    cost *= kRingPenalty[stages];
-    if (best_g == 0 || cost < best_cost) { best_g = g; best_cost = cost; best_stages = stages; }
+    for (int qbuf = 2; qbuf >= 1; --qbuf) {
+      int stages = (budget - fixed - qbuf * g * (int)p.q_tile_bytes) / kv_stage;
+      if (stages > kMaxKvStages) stages = kMaxKvStages;
+      if (stages < 2) continue;
+      const long long groups = (p.B1 + g - 1) / g;
+      const long long items = groups * p.B2 * p.n_qt;
+      const long long rounds = (items + dev.sm_count - 1) / dev.sm_count;
+      // streams alternate between the two softmax warpgroups: an odd count leaves one idle slot.
+      // A CTA's time, in logits-tile times of one warpgroup: per item n_kt tiles for each of its
+      // slots / 2 streams plus about 0.8 for the epilogue and the hand-over to the next item; with
+      // a single Q buffer the next item's Q tiles are loaded and scaled at the hand-over (about 0.5:
+      // each stream's tile is replaced as soon as its last Q K^T has finished).
+      const int slots = (g & 1) ? g + 1 : g;
+      double cost = (double)rounds * (p.n_kt * (slots / 2) + 0.8 + (qbuf == 1 ? 0.5 : 0.0));
+      // a K/V tile takes about two thousand cycles to arrive, most of a logits tile's time: with a
+      // short ring the MMAs wait for their operands (measured: 4 stages cost about 3 %)
+      static const double kRingPenalty[7] = {0, 0, 1.4, 1.15, 1.03, 1.0, 1.0};
+      cost *= kRingPenalty[stages];
+      if (best_g == 0 || cost < best_cost) { best_g = g; best_cost = cost; best_stages = stages; best_qbuf = qbuf; }
+    }
   }
   if (best_g == 0) return AF3K_ERR_BAD_SHAPE;
   p.G = best_g;
   p.kv_stages = best_stages;
+  p.q_buffers = best_qbuf;
   const long long groups = (p.B1 + p.G - 1) / p.G;
   const long long items = groups * p.B2 * p.n_qt;
   if (items > 0x7fffffff) return AF3K_ERR_BAD_SHAPE;
   p.n_items = (int)items;
 
   uint32_t off = 0;
-  p.off_q = off;      off += 2 * p.G * p.q_tile_bytes;
+  p.off_q = off;      off += p.q_buffers * p.G * p.q_tile_bytes;
   p.off_kv = off;     off += p.kv_stages * kv_stage;
   p.off_bias = off;   off += kBiasStages * kBiasTileBytes;
   p.off_bar = off;    off += kBarrierBlockBytes;

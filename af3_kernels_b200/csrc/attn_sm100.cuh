@@ -86,6 +86,7 @@ struct AttnParams {
   int qk_ksteps;         // number of 32-byte K steps of the first GEMM
   int nv;                // N of the second GEMM: D rounded up to 16
   int kv_stages;
+  int q_buffers;         // 2: Q tiles double-buffered by item (the next item's land while this one runs); 1: single
   int qk_is_fp8;
   float scale;           // softmax scale; multiplied by q_scale[h] * k_scale[h] when those are set
   const float* q_scale;
@@ -117,7 +118,7 @@ struct BarIdx {
   static constexpr int bias_empty = 10; // [kBiasStages]
   static constexpr int kv_full = 12;    // [kMaxKvStages]
   static constexpr int kv_empty = 12 + kMaxKvStages;       // P V of the stage's tile finished
-  // Q tiles are double-buffered by item: slot = (item parity) * kMaxStreams + stream
+  // Q tiles: slot = (Q buffer) * kMaxStreams + stream
   static constexpr int q_full = 12 + 2 * kMaxKvStages;       // [2 * kMaxStreams]  Q tile landed
   static constexpr int q_empty = q_full + 2 * kMaxStreams;   // [2 * kMaxStreams]  last Q K^T of the stream finished
   static constexpr int q_scaled = q_empty + 2 * kMaxStreams; // [2 * kMaxStreams]  warp 3 has scaled the Q tile
@@ -201,20 +202,25 @@ __device__ __forceinline__ Item decode_item(const AttnParams& p, int item) {
   return it;
 }
 
+// Q buffer of the CTA's j-th item and how often that buffer was used before.
+__device__ __forceinline__ uint32_t q_buf(const AttnParams& p, uint32_t j) { return p.q_buffers == 2 ? (j & 1u) : 0u; }
+__device__ __forceinline__ uint32_t q_use(const AttnParams& p, uint32_t j) { return p.q_buffers == 2 ? (j >> 1) : j; }
+
 // ------------------------------------------------------------------ producer (one thread)
 __device__ void producer_role(const Ctx& c, const CUtensorMap* tm_q, const CUtensorMap* tm_k,
                               const CUtensorMap* tm_v, const CUtensorMap* tm_bias) {
   const AttnParams& p = *c.p;
   uint32_t ucount = 0, bcount = 0, icount = 0;
   const uint32_t nkv = p.kv_stages;
-  // Q tiles of item j live in buffer j & 1; the tiles of the next item are requested while the
-  // current item runs, so that they are in place (and scaled) when it ends.
+  // With two Q buffers the tiles of the next item are requested while the current item runs, so
+  // that they are in place (and scaled) when it ends; with one (tiles too large for two), as
+  // soon as the current item's K/V loads are all issued.
   auto load_q = [&](const Item& it, uint32_t j) {
-    const uint32_t buf = j & 1;
+    const uint32_t buf = q_buf(p, j), use = q_use(p, j);
     for (int s = 0; s < it.gv; ++s) {
       const int slot = (int)buf * kMaxStreams + s;
-      // the buffer's previous user (item j - 2) must have finished its last Q K^T of this stream
-      if (j >= 2) AF3K_WAIT_NORET(c, BarIdx::q_empty + slot, ((j >> 1) - 1) & 1);
+      // the buffer's previous user must have finished its last Q K^T of this stream
+      if (use >= 1) AF3K_WAIT_NORET(c, BarIdx::q_empty + slot, (use - 1) & 1);
       mbar_arrive_expect_tx(bar_addr(c, BarIdx::q_full + slot), p.q_tile_bytes);
       tma_load_4d(c.smem + p.off_q + (buf * p.G + s) * p.q_tile_bytes, tm_q, bar_addr(c, BarIdx::q_full + slot),
                   0, it.qt * kTile, it.h, it.r0 + s);
@@ -246,7 +252,7 @@ __device__ void producer_role(const Ctx& c, const CUtensorMap* tm_q, const CUten
         tma_load_4d(kdst + p.k_tile_bytes, tm_v, full, 0, kt * kTile, it.h, it.r0 + s);
         ++ucount;
       }
-      if (kt == 0 && item + (int)gridDim.x < p.n_items) {
+      if (kt == (p.q_buffers == 2 ? 0 : p.n_kt - 1) && item + (int)gridDim.x < p.n_items) {
         if (!load_q(decode_item(p, item + gridDim.x), icount + 1)) return;
       }
     }
@@ -285,8 +291,7 @@ __device__ __forceinline__ void mask_values(const AttnParams& p, const Item& it,
 }
 
 // Scaling of Q tiles, cut into 1 KB pieces so that the warp doing it (the P V issuer, which
-// mostly waits) can fit the pieces into its waiting time.  Tiles of item j live in Q buffer
-// j & 1 and land while item j - 1 runs.
+// mostly waits) can fit the pieces into its waiting time.
 struct QScaler {
   uint32_t item = 0, chunk = 0;   // item index (per CTA) of the tiles being scaled, next piece
   int gv = 0, tile = 0;           // tiles that item has, next tile
@@ -297,10 +302,10 @@ struct QScaler {
   __device__ __forceinline__ int step(const Ctx& c, int lane, bool block) {
     const AttnParams& p = *c.p;
     if (tile >= gv) return 0;
-    const uint32_t buf = item & 1;
+    const uint32_t buf = q_buf(p, item);
     const int slot = (int)buf * kMaxStreams + tile;
     if (chunk == 0) {
-      const uint32_t par = (item >> 1) & 1;
+      const uint32_t par = q_use(p, item) & 1;
       bool ok = mbar_test_wait(bar_addr(c, BarIdx::q_full + slot), par);
       if (!__all_sync(0xffffffffu, ok)) {
         if (!block) return 0;
@@ -438,11 +443,11 @@ __device__ void qk_issuer_role(const Ctx& c) {
           if (!first[0]) { AF3K_WAIT_WARP(c, BarIdx::s_free + 0, sfree_par[0]); sfree_par[0] ^= 1; }
           first[0] = 0;
         }
-        const int qslot = (int)(icount & 1) * kMaxStreams + s;   // Q tiles are double-buffered by item
-        if (kt == 0) AF3K_WAIT_WARP(c, (kTcBias ? BarIdx::q_scaled : BarIdx::q_full) + qslot, (icount >> 1) & 1);
+        const int qslot = (int)q_buf(p, icount) * kMaxStreams + s;
+        if (kt == 0) AF3K_WAIT_WARP(c, (kTcBias ? BarIdx::q_scaled : BarIdx::q_full) + qslot, q_use(p, icount) & 1);
         AF3K_WAIT_WARP(c, BarIdx::kv_full + st, kv_par);
         tc_fence_after();
-        const uint32_t a_lo = qd_lo + ((icount & 1) * p.G + s) * q_step;
+        const uint32_t a_lo = qd_lo + (q_buf(p, icount) * p.G + s) * q_step;
         const uint32_t b_lo = kd_lo + st * stage_step;
         const uint32_t s_tmem = c.tmem + kSCol + b * kTile;
         const uint32_t slot16 = st * (kMaskPanelBytes >> 4);

@@ -61,7 +61,7 @@ typedef struct af3k_attention_desc {
   int32_t qk_dtype;       /* AF3K_BF16 or AF3K_FP8_E4M3 */
   int32_t bias_dtype;     /* AF3K_BF16 or AF3K_F32 */
   float softmax_scale;    /* the reference uses 1/sqrt(D) */
-  int32_t rows_per_item;  /* 0 = choose; else requested pair rows per staged bias tile (1..8, clamped to what fits) */
+  int32_t rows_per_item;  /* 0 = choose; else requested pair rows per staged bias tile (1..8, clamped to what fits, at most 4) */
 } af3k_attention_desc;
 
 /* Library / ABI version (major * 1000 + minor). */
@@ -86,6 +86,9 @@ size_t af3k_dot_product_attention_workspace(const af3k_attention_desc* desc, con
  * Differences a caller sees: inputs are never written (the reference overwrites q), the result
  * goes to a caller-provided `out`, masked keys are a byte predicate instead of an additive
  * -1e9 tensor, and errors come back as codes instead of exit(1).
+ * Rounding points with bf16 q/k: q * softmax_scale is rounded to bf16 before the first GEMM (as
+ * in the reference); logits, bias add and softmax are fp32 (the reference rounds the logits to
+ * bf16); the weights are rounded to bf16 for the second GEMM (as in the reference).
  *
  * mask may be NULL (no key is masked).  q_scale / k_scale must be NULL for bf16 q/k.
  * status_dev may be NULL; otherwise it must point at int[4] the caller zeroed: [0] is OR-ed
@@ -139,9 +142,10 @@ void af3k_set_wait_limit_cycles(long long cycles);
 int af3k_describe_plan(const af3k_attention_desc* desc, int32_t* out6);
 
 /* Diagnostic: when dump_dev is non-NULL, later attention calls run a debug build of the kernel
- * that writes block 0's first logits tile to dump_dev (4 * 128 * 128 floats: raw logits, packed
- * P words, un-normalised O, {max, sum}).  Pass NULL to switch it off.  No counterpart in the
- * reference. */
+ * that writes block 0's first logits tile to dump_dev (4 * 128 * 128 floats: logits as the
+ * tensor core delivers them - with bf16 q/k that is scale * q k^T + bias + mask value -, packed
+ * P words, un-normalised O, {max, sum}), followed by 2 * (2 * 256 * 8 + 4 * 256) floats of
+ * SM-clock stamps.  Pass NULL to switch it off.  No counterpart in the reference. */
 void af3k_debug_set_dump(float* dump_dev);
 
 /* Self-test of the bounded wait: launches one block that waits, with the given limit, on a
