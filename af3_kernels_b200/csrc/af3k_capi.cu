@@ -333,7 +333,8 @@ const char* af3k_strerror(int code) {
 
 size_t af3k_dot_product_attention_workspace(const af3k_attention_desc* desc, const void* bias) {
   if (desc == nullptr || validate(*desc) != AF3K_OK) return 0;
-  if (!bias_needs_staging(*desc, bias)) return 0;
+  // fp8 q/k: the staging copy is what lets the tensor core add the bias (optional, see the entry)
+  if (!bias_needs_staging(*desc, bias) && desc->qk_dtype != AF3K_FP8_E4M3) return 0;
   return (size_t)desc->B2 * desc->Sq * staged_bias_pitch(desc->Sk) * 2;
 }
 
@@ -373,22 +374,31 @@ int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, c
   const void* bias_base = bias;
   int64_t bias_sh = d.bias_stride[0], bias_sr = d.bias_stride[1];
   int launches = 0;
-  if (bias_needs_staging(d, bias)) {
+  // fp8 q/k: with a staging copy divided by the head's logit scale the tensor core adds the bias
+  // to the raw fp8 products (the fast kernel); without room for one the softmax threads add the
+  // bias in fp32 as before
+  const size_t stage_bytes = (size_t)d.B2 * d.Sq * staged_bias_pitch(d.Sk) * 2;
+  const bool must_stage = bias_needs_staging(d, bias);
+  const bool fp8_tc = fp8 && workspace != nullptr && workspace_bytes >= stage_bytes && aligned16(workspace);
+  if (must_stage || fp8_tc) {
     const int64_t pitch = staged_bias_pitch(d.Sk);
-    const size_t need = (size_t)d.B2 * d.Sq * pitch * 2;
+    const size_t need = stage_bytes;
     if (workspace == nullptr || workspace_bytes < need) return AF3K_ERR_WORKSPACE;
     if (!aligned16(workspace)) return AF3K_ERR_BAD_ALIGNMENT;
+    const float* sq = fp8_tc ? q_scale : nullptr;
+    const float* sk = fp8_tc ? k_scale : nullptr;
     const long long total = (long long)d.B2 * d.Sq * (pitch / 2);
     int blocks = (int)((total + 255) / 256);
     if (blocks > dev->sm_count * 16) blocks = dev->sm_count * 16;
     if (d.bias_dtype == AF3K_F32)
       bias_to_bf16_kernel<float><<<blocks, 256, 0, stream>>>(
           static_cast<const float*>(bias), static_cast<__nv_bfloat16*>(workspace), (int)d.B2,
-          (int)d.Sq, (int)d.Sk, d.bias_stride[0], d.bias_stride[1], (int)pitch);
+          (int)d.Sq, (int)d.Sk, d.bias_stride[0], d.bias_stride[1], (int)pitch, sq, sk, d.softmax_scale);
     else
       bias_to_bf16_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
           static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(workspace),
-          (int)d.B2, (int)d.Sq, (int)d.Sk, d.bias_stride[0], d.bias_stride[1], (int)pitch);
+          (int)d.B2, (int)d.Sq, (int)d.Sk, d.bias_stride[0], d.bias_stride[1], (int)pitch, sq, sk,
+          d.softmax_scale);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail("launch bias_to_bf16_kernel", e);
     ++launches;
@@ -416,9 +426,10 @@ int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, c
   p.wait_limit = wait_limit_cycles();
 
   p.debug = g_debug_dump.load();
-  // bf16 q/k: scale, bias and mask all come out of the tensor core; fp8 q/k: the softmax threads
-  // apply the (inexact-in-bf16) de-quantisation scale and the bias in fp32
-  const bool tc_bias = !p.qk_is_fp8;
+  // scale, bias and mask all come out of the tensor core, except for fp8 q/k without a staging
+  // copy of the bias: there the softmax threads apply scale and bias in fp32
+  const bool tc_bias = !fp8 || fp8_tc;
+  p.scale_q = fp8 ? 0 : 1;
   const bool dbg = p.debug != nullptr;
   if (dbg && tc_bias)
     attention_kernel<true, true><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
@@ -473,7 +484,10 @@ int af3k_dot_product_attention_noalloc(const af3k_attention_desc* desc, const vo
   if (desc == nullptr) return AF3K_ERR_NULL_POINTER;
   int rc = validate(*desc);
   if (rc != AF3K_OK) return rc;
-  const size_t need = af3k_dot_product_attention_workspace(desc, bias);
+  // the staging copy is required for a bias TMA cannot read in place, optional (faster kernel)
+  // for fp8 q/k: an optional copy that does not fit is simply not made
+  size_t need = af3k_dot_product_attention_workspace(desc, bias);
+  if (need > kStaticScratchBytes && !bias_needs_staging(*desc, bias)) need = 0;
   if (need > kStaticScratchBytes) {
     std::snprintf(t_detail, sizeof(t_detail),
                   "bias staging copy needs %zu bytes, the built-in scratch holds %zu", need,

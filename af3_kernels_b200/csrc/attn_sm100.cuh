@@ -31,9 +31,12 @@
 //     keys (what "fill with -1e9, then softmax" gives), a key that does not exist with weight 0.
 //
 // What is left per logit is a maximum, one fused multiply-add, the exponential, the row sum and
-// the bf16 rounding of P.  With fp8 q/k the de-quantisation factors are not exact in bf16, so
-// scale and bias are applied by the softmax threads in fp32 (the bias tile is read from shared
-// memory); the mask column is used either way.
+// the bf16 rounding of P.  With fp8 q/k the logit scale t = softmax scale x the two
+// de-quantisation factors cannot be folded into Q; there the bias staging pass divides the bias
+// by t, the tensor core adds it to the raw fp8 products, the masked-key value is enlarged by 1/t,
+// and t rides on the fused multiply-add.  When the caller gives no room for that staging copy
+// the second instantiation of the kernel runs, in which the softmax threads apply t and add the
+// bias in fp32 from the staged tile in shared memory; the mask column is used either way.
 //
 // Logits stay fp32 from the tensor core to the exponential; P is rounded to bf16 once, when it
 // is written to TMEM as the A operand of the second GEMM.  S and P live in separate TMEM columns:
@@ -88,6 +91,7 @@ struct AttnParams {
   int kv_stages;
   int q_buffers;         // 2: Q tiles double-buffered by item (the next item's land while this one runs); 1: single
   int qk_is_fp8;
+  int scale_q;           // 1: bf16 q/k, the Q tiles are multiplied by `scale` in shared memory
   float scale;           // softmax scale; multiplied by q_scale[h] * k_scale[h] when those are set
   const float* q_scale;
   const float* k_scale;
@@ -280,14 +284,24 @@ __device__ __forceinline__ void scale_q_chunk(uint32_t addr, float scale, int la
 
 // The 128 mask-column values (bf16) of one logits tile, four per lane.
 __device__ __forceinline__ void mask_values(const AttnParams& p, const Item& it, int kt, int s, int lane,
-                                            uint16_t (&val)[4]) {
+                                            uint16_t masked, uint16_t (&val)[4]) {
   const uint8_t* mrow = p.mask != nullptr ? p.mask + (long long)(it.r0 + s) * p.mask_row_stride : nullptr;
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     const int key = kt * kTile + 32 * g + lane;
-    val[g] = key >= p.Sk ? kMaskColAbsent
-                         : ((mrow == nullptr || mrow[key] != 0) ? kMaskColKeep : kMaskColMasked);
+    val[g] = key >= p.Sk ? kMaskColAbsent : ((mrow == nullptr || mrow[key] != 0) ? kMaskColKeep : masked);
   }
+}
+
+// bf16 bits of the value a masked key gets for head h.  The tensor core's logits are multiplied
+// by the head's logit scale t afterwards when that scale is not folded into Q (fp8 q/k), so the
+// value is -2^(47 + ceil(-log2 t)) there: still -2^47 or beyond after the multiplication.
+__device__ __forceinline__ uint16_t masked_value_bits(const AttnParams& p, int h) {
+  if (p.q_scale == nullptr) return kMaskColMasked;
+  const float t = p.scale * p.q_scale[h] * p.k_scale[h];
+  int e = 47 - min(0, ilogbf(t));
+  e = min(e, 120);
+  return (uint16_t)(0x8000u | ((uint32_t)(e + 127) << 7));
 }
 
 // Scaling of Q tiles, cut into 1 KB pieces so that the warp doing it (the P V issuer, which
@@ -355,14 +369,15 @@ __device__ void mask_writer_role(const Ctx& c, int lane) {
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x) {
     const Item it = decode_item(p, item);
     uint16_t val[4];
-    mask_values(p, it, 0, 0, lane, val);
+    const uint16_t masked = masked_value_bits(p, it.h);
+    mask_values(p, it, 0, 0, lane, masked, val);
     for (int kt = 0; kt < p.n_kt; ++kt) {
       for (int s = 0; s < it.gv; ++s) {
         const uint16_t cur[4] = {val[0], val[1], val[2], val[3]};
         {
           const int ns = s + 1 < it.gv ? s + 1 : 0;
           const int nkt = s + 1 < it.gv ? kt : kt + 1;
-          if (nkt < p.n_kt) mask_values(p, it, nkt, ns, lane, val);
+          if (nkt < p.n_kt) mask_values(p, it, nkt, ns, lane, masked, val);
         }
         if (round > 0) AF3K_WAIT_WARP(c, BarIdx::kv_empty + st, (round - 1) & 1);
         const uint32_t slot = c.smem + p.off_mcol + st * kMaskPanelBytes;
@@ -444,7 +459,7 @@ __device__ void qk_issuer_role(const Ctx& c) {
           first[0] = 0;
         }
         const int qslot = (int)q_buf(p, icount) * kMaxStreams + s;
-        if (kt == 0) AF3K_WAIT_WARP(c, (kTcBias ? BarIdx::q_scaled : BarIdx::q_full) + qslot, q_use(p, icount) & 1);
+        if (kt == 0) AF3K_WAIT_WARP(c, (p.scale_q ? BarIdx::q_scaled : BarIdx::q_full) + qslot, q_use(p, icount) & 1);
         AF3K_WAIT_WARP(c, BarIdx::kv_full + st, kv_par);
         tc_fence_after();
         const uint32_t a_lo = qd_lo + (q_buf(p, icount) * p.G + s) * q_step;
@@ -496,7 +511,7 @@ __device__ void pv_issuer_role(const Ctx& c, int lane) {
   const AttnParams& p = *c.p;
   const bool leader = elect_one();
   QScaler scaler;
-  if (kTcBias && (int)blockIdx.x < p.n_items) {
+  if (kTcBias && p.scale_q && (int)blockIdx.x < p.n_items) {
     scaler.start(0, decode_item(p, blockIdx.x).gv);
     while (scaler.pending())
       if (scaler.step(c, lane, true) < 0) return;
@@ -520,7 +535,7 @@ __device__ void pv_issuer_role(const Ctx& c, int lane) {
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
     const Item it = decode_item(p, item);
     const int gv = it.gv;
-    scaler.start(icount + 1, (kTcBias && item + (int)gridDim.x < p.n_items) ? decode_item(p, item + gridDim.x).gv : 0);
+    scaler.start(icount + 1, (kTcBias && p.scale_q && item + (int)gridDim.x < p.n_items) ? decode_item(p, item + gridDim.x).gv : 0);
     for (int kt = 0; kt < p.n_kt; ++kt) {
       for (int s = 0; s < gv; ++s) {
         const int b = s & 1;
@@ -637,16 +652,19 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
 
   const float mt = fmaxf(mxa, mxb);
   if (ts != nullptr) ts[2] = clock64() + (long long)(mt == 123.456f);   // after the logits pass
+  // factor between a logit difference and the exponent of 2: log2(e), times the logit scale when
+  // the tensor core's logits still lack it (fp8 q/k with tensor-core bias: `scale` carries it)
+  const float ef = kTcBias ? scale : kLog2e;
   float m_use = m_run;
   float alpha = 1.0f;
   bool need = false;
   if (first_kt) {
     m_use = mt;
   } else {
-    need = (mt - m_run) * kLog2e > kLazyRescaleLog2;
+    need = (mt - m_run) * ef > kLazyRescaleLog2;
     if (need) {
       m_use = mt;
-      alpha = ex2_approx((m_run - mt) * kLog2e);
+      alpha = ex2_approx((m_run - mt) * ef);
     }
   }
   if (ts != nullptr) ts[3] = clock64();   // row maximum known
@@ -658,9 +676,9 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
   // any of its warps overlaps with that (measured), so a tile costs 128 x 8 cycles plus its
   // FMA-pipe instructions, while ALU-pipe work (the maximum, the bf16 packing) is free.  The
   // packed f32x2 forms halve the FMA-pipe instruction count at the same cost per value.
-  const uint64_t l2e2 = pack_f32x2(kLog2e, kLog2e);
+  const uint64_t l2e2 = pack_f32x2(ef, ef);
   const uint64_t nm2 = pack_f32x2(-m_use, -m_use);
-  const float nml = -m_use * kLog2e;
+  const float nml = -m_use * ef;
   const uint64_t nml2 = pack_f32x2(nml, nml);
   uint64_t suma = pack_f32x2(0.f, 0.f), sumb = suma;
   // The first kHeld column groups are computed before anything is written: the P buffer and the
@@ -746,8 +764,11 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
 
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
     const Item it = decode_item(p, item);
+    // fp32 path: the logit scale the softmax threads apply themselves.  Tensor-core path: the
+    // factor from logit differences to exponents of 2 (the scale is in Q already for bf16 q/k)
     float scale = p.scale;
     if (p.q_scale != nullptr) scale *= p.q_scale[it.h] * p.k_scale[it.h];
+    if (kTcBias) scale = (p.scale_q ? 1.0f : scale) * kLog2e;
 
     long long* last_ts = nullptr;     // debug build: timeline slot of the warpgroup's last tile
     for (int kt = 0; kt < p.n_kt; ++kt) {
@@ -951,10 +972,14 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
 
 // ------------------------------------------------------------------ bias staging pre-pass
 // bias (fp32 or bf16, arbitrary row pitch) -> bf16 [B2, Sq, pitch] with a TMA-legal pitch.
+// With fp8 q/k (q_scale / k_scale given) every value is divided by the head's logit scale
+// softmax_scale * q_scale[h] * k_scale[h]: the tensor core then adds it to the raw fp8 products
+// and the softmax threads apply that scale to the sum.
 template <typename T>
 __global__ void bias_to_bf16_kernel(const T* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                     int B2, int Sq, int Sk, long long src_stride_h,
-                                    long long src_stride_r, int pitch) {
+                                    long long src_stride_r, int pitch, const float* __restrict__ q_scale,
+                                    const float* __restrict__ k_scale, float softmax_scale) {
   const long long total = (long long)B2 * Sq * (pitch / 2);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -963,9 +988,10 @@ __global__ void bias_to_bf16_kernel(const T* __restrict__ src, __nv_bfloat16* __
     const int r = (int)(t % Sq);
     const int h = (int)(t / Sq);
     const T* s = src + h * src_stride_h + r * src_stride_r;
+    const float mul = q_scale != nullptr ? 1.0f / (softmax_scale * q_scale[h] * k_scale[h]) : 1.0f;
     const int col = cp * 2;
-    const float a = col < Sk ? (float)s[col] : 0.f;
-    const float b = col + 1 < Sk ? (float)s[col + 1] : 0.f;
+    const float a = col < Sk ? (float)s[col] * mul : 0.f;
+    const float b = col + 1 < Sk ? (float)s[col + 1] * mul : 0.f;
     reinterpret_cast<uint32_t*>(dst)[i] = pack_bf16x2(a, b);
   }
 }

@@ -75,12 +75,16 @@ def dot_product_attention(
     rows_per_item: int = 0,
     out: Optional[torch.Tensor] = None,
     check_status: Optional[bool] = None,
+    use_workspace: bool = True,
 ) -> torch.Tensor:
     """softmax(scale * q k^T + bias, key-masked) v on the current CUDA stream.
 
     q, k, v: [B1, B2, S, D] on one CUDA device.  q/k bf16, or float8_e4m3fn with per-head fp32
     ``q_scale`` / ``k_scale`` [B2].  v bf16.  bias: B2*Sq*Sk elements, bf16 or fp32, shared by
     every b1.  mask: see ``_mask_rows``.  Returns a new bf16 tensor; inputs are not modified.
+    ``use_workspace=False`` hands the library no scratch: a bias that needs a staging copy (fp32, or
+    rows that are not 16-byte aligned) is then refused, and fp8 q/k run on the kernel variant whose
+    softmax threads add the bias themselves.
     """
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
         raise ValueError("q, k, v must be 4-D [B1, B2, S, D]")
@@ -146,6 +150,8 @@ def dot_product_attention(
     lib = _capi.load()
     with torch.cuda.device(q.device):
         ws_bytes = lib.af3k_dot_product_attention_workspace(ctypes.byref(desc), bias.data_ptr())
+        if not use_workspace:
+            ws_bytes = 0
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
         status = _status_buffer(q.device)
         code = lib.af3k_dot_product_attention(

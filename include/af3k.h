@@ -74,8 +74,10 @@ const char* af3k_strerror(int code);
  * ("" if none failed yet).  Never NULL. */
 const char* af3k_last_error_detail(void);
 
-/* Bytes of device scratch af3k_dot_product_attention needs for this problem (0 if none):
- * the bf16 staging copy of a bias that is fp32 or whose row pitch TMA cannot address. */
+/* Bytes of device scratch af3k_dot_product_attention can use for this problem (0 if none): the
+ * bf16 staging copy of the bias.  It is required for a bias that is fp32 or whose row pitch TMA
+ * cannot address (AF3K_ERR_WORKSPACE without it); with fp8 q/k it is optional and selects the
+ * faster kernel, in which the tensor core adds the (pre-scaled) bias. */
 size_t af3k_dot_product_attention_workspace(const af3k_attention_desc* desc, const void* bias);
 
 /* out = softmax(scale * q k^T + bias, key-masked) v

@@ -111,6 +111,33 @@ def test_cfg5_fp8_reduced_rows(cuda_device):
     assert st["nan"] == 0 and st["max_abs"] <= FP8_MAX_ABS, st
 
 
+def test_fp8_both_kernel_variants(cuda_device):
+    """fp8 q/k run on two kernels: with a workspace the bias (divided by the head's logit scale in
+    the staging pass) is added by the tensor core, without one the softmax threads add it in
+    fp32.  Both against the de-quantised fp32 oracle, with small and with tiny quantisation
+    scales (the value a masked key gets is scaled with them), and a fully masked row."""
+    g = torch.Generator().manual_seed(77)
+    B1, B2, S, D = 3, 2, 296, 32          # bias rows of 592 bytes: usable in place, no staging needed
+    for amp in (1.0, 1e-3):
+        qf = torch.randn(B1, B2, S, D, generator=g) * amp
+        kf = torch.randn(B1, B2, S, D, generator=g) * amp
+        v = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+        bias = torch.randn(B2, S, S, generator=g).to(torch.bfloat16)
+        mask = torch.rand(B1, S, generator=g) >= 0.1
+        mask[1, :] = False
+        q, qs = O.quantize_e4m3_per_head(qf)
+        k, ks = O.quantize_e4m3_per_head(kf)
+        ref = O.oracle_fp32(q, k, v, mask, bias, q_scale=qs, k_scale=ks)
+        for use_ws in (True, False):
+            out = _run(cuda_device, q, k, v, mask, bias, q_scale=qs, k_scale=ks, use_workspace=use_ws)
+            st = O.error_stats(out, ref)
+            assert st["nan"] == 0 and st["max_abs"] <= FP8_MAX_ABS, (amp, use_ws, st)
+            uniform = v[1].float().mean(dim=1, keepdim=True).expand(B2, S, D)
+            assert (out[1].float() - uniform).abs().max().item() <= 1e-2, (amp, use_ws)
+            lib = _capi.load()
+            assert lib.af3k_last_launch_count() == (2 if use_ws else 1)
+
+
 def test_cfg5_fp8_quarter_size_properties(cuda_device):
     dev = cuda_device
     g = torch.Generator(device=dev).manual_seed(0)
