@@ -11,6 +11,7 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from . import pair_bias
 from .fused_ops import attention_block
 from .tools import pad_to_size, profile, record_comm_time
 
@@ -38,19 +39,25 @@ class GridSelfAttentionCpp(nn.Module):
                 self.gating_query.weight.T, self.output_projection.weight.T)
 
     def _norm_and_bias(self, pair: torch.Tensor):
+        # c_pair = 128: one fused pass (LayerNorm, bias projection, permute); other widths go
+        # through PyTorch's LayerNorm and Linear on the same device
+        if pair_bias.supported(pair, self.num_head):
+            return pair_bias.layernorm_pair_bias(pair, self.act_norm.weight, self.act_norm.bias,
+                                                 self.pair_bias_projection.weight, self.act_norm.eps)
         pair = self.act_norm(pair)
         bias = self.pair_bias_projection(pair).permute(2, 0, 1)     # [H, N, N]
         return pair, bias
 
     @profile("B200 GridSelfAttention")
     def forward(self, pair: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        dtype = pair.dtype
         pair, bias = self._norm_and_bias(pair)
         if self.transpose:
             pair = pair.permute(1, 0, 2)
         out = attention_block(pair, mask, bias, *self._weights(), self.num_head)
         if self.transpose:
             out = out.permute(1, 0, 2)
-        return out
+        return out.to(dtype)
 
 
 class DistributedGridSelfAttentionCpp(GridSelfAttentionCpp):
@@ -67,6 +74,7 @@ class DistributedGridSelfAttentionCpp(GridSelfAttentionCpp):
     @profile("B200 Distributed GridSelfAttention")
     def forward(self, pair: torch.Tensor, mask: torch.Tensor, COMM_SPLIT: int = 4) -> torch.Tensor:
         rk, ws = dist.get_rank(), dist.get_world_size()
+        dtype = pair.dtype
         seq_len = pair.shape[0]
         split_size = ceil(seq_len / ws)
         rows = slice(split_size * rk, split_size * (rk + 1))
@@ -103,4 +111,4 @@ class DistributedGridSelfAttentionCpp(GridSelfAttentionCpp):
         out = gathered.view(ws * split_size, *pair.shape[1:])[:seq_len]
         if self.transpose:
             out = out.permute(1, 0, 2)
-        return out.contiguous()
+        return out.contiguous().to(dtype)

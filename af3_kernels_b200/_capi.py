@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "af3k_describe_plan",
     "af3k_debug_set_dump",
     "af3k_selftest_wait_timeout",
+    "af3k_pair_bias",
 )
 
 
@@ -102,6 +103,9 @@ def load() -> ctypes.CDLL:
     lib.af3k_debug_set_dump.argtypes = [vp]
     lib.af3k_selftest_wait_timeout.restype = ctypes.c_int
     lib.af3k_selftest_wait_timeout.argtypes = [i64, vp, vp]
+    lib.af3k_pair_bias.restype = ctypes.c_int
+    lib.af3k_pair_bias.argtypes = [vp, ctypes.c_int32, i64, i64, i64, i64, vp, vp, vp, ctypes.c_float, vp, vp,
+                                   i64, vp]
     _lib = lib
     return lib
 

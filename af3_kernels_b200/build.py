@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libaf3k.so")
 SOURCES = [os.path.join(CSRC, "af3k_capi.cu")]
 HEADERS = [
     os.path.join(CSRC, "attn_sm100.cuh"),
+    os.path.join(CSRC, "pair_bias_sm100.cuh"),
     os.path.join(CSRC, "ptx_sm100.cuh"),
     os.path.join(_HERE, "..", "include", "af3k.h"),
 ]

@@ -12,6 +12,7 @@
 #include <cudaTypedefs.h>
 
 #include "attn_sm100.cuh"
+#include "pair_bias_sm100.cuh"
 
 namespace {
 
@@ -501,6 +502,46 @@ int af3k_dot_product_attention_noalloc(const af3k_attention_desc* desc, const vo
   // previous call's contents needs clearing.
   return af3k_dot_product_attention(desc, q, k, v, bias, mask, out, q_scale, k_scale, scratch,
                                     need != 0 ? kStaticScratchBytes : 0, status_dev, stream);
+}
+
+int af3k_pair_bias(const void* pair, int32_t pair_dtype, int64_t R, int64_t N, int64_t C, int64_t H,
+                   const float* gamma, const float* beta, const float* proj, float eps, void* normed,
+                   void* bias, int64_t bias_pitch, void* stream_v) {
+  t_last_launches = 0;
+  if (pair_dtype != AF3K_BF16 && pair_dtype != AF3K_F32) return AF3K_ERR_BAD_DTYPE;
+  if (C != kPbChannels || H < 1 || H > kPbMaxHeads || R < 0 || N < 0 || R > 0x7fffffff || N > 0x7fffffff)
+    return AF3K_ERR_BAD_SHAPE;
+  if (bias_pitch < N || (bias_pitch & 7) != 0) return AF3K_ERR_BAD_STRIDE;
+  if (R == 0 || N == 0) return AF3K_OK;
+  if (!pair || !gamma || !beta || !proj || !normed || !bias) return AF3K_ERR_NULL_POINTER;
+  if (!aligned16(pair) || !aligned16(normed) || !aligned16(bias)) return AF3K_ERR_BAD_ALIGNMENT;
+  DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev);
+  if (rc != AF3K_OK) return rc;
+  PairBiasParams p;
+  p.pair = pair; p.normed = static_cast<__nv_bfloat16*>(normed); p.bias = static_cast<__nv_bfloat16*>(bias);
+  p.gamma = gamma; p.beta = beta; p.proj = proj;
+  p.R = (int)R; p.N = (int)N; p.H = (int)H; p.bias_pitch = bias_pitch; p.eps = eps;
+  // persistent CTAs, one per SM, over R * ceil(N / 128) tiles
+  const long long n_tiles = R * ((N + kPbTileJ - 1) / kPbTileJ);
+  const long long max_ctas = dev->sm_count;
+  const unsigned grid = (unsigned)(n_tiles < max_ctas ? n_tiles : max_ctas);
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  const bool f32 = pair_dtype == AF3K_F32;
+  if (H <= 4) {
+    if (f32) pair_bias_kernel_h4<float><<<grid, kPbThreads, 0, stream>>>(p);
+    else     pair_bias_kernel_h4<__nv_bfloat16><<<grid, kPbThreads, 0, stream>>>(p);
+  } else if (H <= 8) {
+    if (f32) pair_bias_kernel<float, 8><<<grid, kPbThreads, 0, stream>>>(p);
+    else     pair_bias_kernel<__nv_bfloat16, 8><<<grid, kPbThreads, 0, stream>>>(p);
+  } else {
+    if (f32) pair_bias_kernel<float, 16><<<grid, kPbThreads, 0, stream>>>(p);
+    else     pair_bias_kernel<__nv_bfloat16, 16><<<grid, kPbThreads, 0, stream>>>(p);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail("launch pair_bias_kernel", e);
+  t_last_launches = 1;
+  return AF3K_OK;
 }
 
 int af3k_selftest_wait_timeout(long long limit_cycles, int* status_dev, void* stream_v) {

@@ -182,7 +182,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2",
-                    choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "grid_block"])
+                    choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "grid_block", "pair_bias"])
     ap.add_argument("--rows", type=int, default=0, help="override pair rows per GPU (debugging)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--kernel-only", action="store_true",
@@ -212,9 +212,9 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     name = args.workload
-    if name == "grid_block":
+    if name in ("grid_block", "pair_bias"):
         if rank == 0:
-            grid_block_line(args, dev)
+            (grid_block_line if name == "grid_block" else pair_bias_line)(args, dev)
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
@@ -421,6 +421,56 @@ def grid_block_line(args, dev):
                       "ms_per_step": ms, "attention_flops": attn_flops, "projection_flops": gemm_flops,
                       "config": {"workload": f"GridSelfAttentionCpp forward, pair [{N},{N},{C}] bf16, {H} heads"},
                       "dtype": "bf16", "data": "synthetic"}), flush=True)
+
+
+def pair_bias_line(args, dev):
+    """Extra workload (not the headline line): the fused pair-bias producer (LayerNorm + bias
+    projection + permute) on a device-resident pair [N, N, 128] bf16, N = 768, 4 heads.  HBM-bound:
+    algorithmic bytes = pair read + normalised pair written (2 bytes per element each) + bias."""
+    import ctypes
+    from af3_kernels_b200 import _capi
+    N, C, H = (args.rows or 768), 128, 4
+    g = torch.Generator(device=dev).manual_seed(0)
+    pair = torch.randn(N, N, C, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    ln_w = torch.ones(C, device=dev)
+    ln_b = torch.zeros(C, device=dev)
+    w = torch.randn(H, C, generator=g, device=dev) * 0.1
+    pitch = (N + 7) // 8 * 8
+    # three sets of buffers in rotation so that a launch does not find its input in L2; the C entry
+    # point is called directly (the Python wrapper's allocations would be timed otherwise)
+    sets = [(pair.clone(), torch.empty_like(pair), torch.empty((H, N, pitch), dtype=torch.bfloat16, device=dev))
+            for _ in range(3)]
+    lib = _capi.load()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def launch(i):
+        src, normed, bias = sets[i % 3]
+        _capi.check(lib.af3k_pair_bias(src.data_ptr(), _capi.AF3K_BF16, N, N, C, H, ln_w.data_ptr(),
+                                       ln_b.data_ptr(), w.data_ptr(), ctypes.c_float(1e-5),
+                                       normed.data_ptr(), bias.data_ptr(), pitch, stream))
+
+    for i in range(max(args.warmup, 3)):
+        launch(i)
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for i, (e0, e1) in enumerate(evs):
+        e0.record()
+        launch(i)
+        e1.record()
+    torch.cuda.synchronize()
+    ms = sum(e0.elapsed_time(e1) for e0, e1 in evs) / len(evs)
+    alg_bytes = 2.0 * N * N * C * 2 + 2.0 * H * N * ((N + 7) // 8 * 8)
+    peaks = load_peaks()
+    gbs = alg_bytes / (ms / 1e3) / 1e9
+    print(json.dumps({"metric": "pair_bias_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "ms_per_step": ms,
+                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                   "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                                   "kernel": "pair_bias_kernel", "algorithmic_bytes_per_launch": alg_bytes,
+                                   "traffic": None},
+                      "config": {"workload": f"pair-bias producer, pair [{N},{N},{C}] bf16 -> normed bf16 + bias [{H},{N},{N}] bf16",
+                                 "cache": "three buffer sets in rotation (920 MB > L2)"},
+                      "dtype": "f32", "data": "synthetic"}), flush=True)
 
 
 # DRAM bytes per launch of attention_kernel from one ncu capture (dram__bytes_read.sum +

@@ -150,6 +150,24 @@ int af3k_describe_plan(const af3k_attention_desc* desc, int32_t* out6);
  * SM-clock stamps.  Pass NULL to switch it off.  No counterpart in the reference. */
 void af3k_debug_set_dump(float* dump_dev);
 
+/* Pair-bias producer: LayerNorm over the 128 channels of the pair representation, the per-head
+ * bias projection and the [N, N, H] -> [H, N, N] permute, in one pass.
+ *
+ * Stands in for the two statements in front of the attention core in the reference's modules,
+ *     pair = self.act_norm(pair); bias = self.pair_bias_projection(pair).permute(2, 0, 1)
+ * (src/af3_kernels/Attention.py:51-52 and :152-153).
+ *
+ *   pair    [R, N, 128] contiguous, pair_dtype AF3K_BF16 or AF3K_F32
+ *   gamma, beta [128] fp32 (LayerNorm weight and bias), proj [H, 128] fp32 (nn.Linear weight)
+ *   normed  [R, N, 128] bf16: the normalised pair (operand of the q / k / v / gate projections)
+ *   bias    [H, R, bias_pitch] bf16, bias_pitch >= N and a multiple of 8: element (h, i, j) is the
+ *           logit bias of head h between positions i and j, bias[h][i][j] =
+ *           sum_c bf16(normed[i][j][c]) * proj[h][c]; pad columns are not written
+ * 1 <= H <= 16.  All pointers 16-byte aligned.  stream is a cudaStream_t. */
+int af3k_pair_bias(const void* pair, int32_t pair_dtype, int64_t R, int64_t N, int64_t C, int64_t H,
+                   const float* gamma, const float* beta, const float* proj, float eps, void* normed,
+                   void* bias, int64_t bias_pitch, void* stream);
+
 /* Self-test of the bounded wait: launches one block that waits, with the given limit, on a
  * barrier nothing ever arrives at, and writes AF3K_STATUS_WAIT_TIMEOUT to status_dev when the
  * wait gives up.  No counterpart in the reference (it has no device code). */

@@ -191,6 +191,16 @@ def error_stats(out: torch.Tensor, ref: torch.Tensor) -> dict:
 
 
 # ----------------------------------------------------------------------------- blocks
+def pair_bias_fp32(pair, ln_w, ln_b, w_bias, eps=1e-5):
+    """fp32 restatement of the two statements in front of the attention core in the reference's
+    modules (src/af3_kernels/Attention.py:51-52 and :152-153; the same lines of the PyTorch models
+    in examples/grid_self_attention.py): LayerNorm over the channels, then the per-head bias
+    projection permuted to [H, R, N].  Returns (normalised pair [R, N, C], bias [H, R, N])."""
+    F = torch.nn.functional
+    x = F.layer_norm(pair.float(), (pair.shape[-1],), ln_w.float(), ln_b.float(), eps)
+    return x, F.linear(x, w_bias.float()).permute(2, 0, 1)
+
+
 def grid_block_fp32(pair, mask, ln_w, ln_b, w_bias, w_q, w_k, w_v, w_gate, w_out, num_head,
                     transpose=False, eps=1e-5) -> torch.Tensor:
     """fp32 restatement of the reference's PyTorch grid self-attention model
@@ -198,8 +208,7 @@ def grid_block_fp32(pair, mask, ln_w, ln_b, w_bias, w_q, w_k, w_v, w_gate, w_out
     projection, q/k/v projections, biased key-masked attention, sigmoid gate, output projection.
     All weights as ``nn.Linear.weight`` ([out, in]).  pair [N, N, C], mask [N, N] -> [N, N, C]."""
     F = torch.nn.functional
-    x = F.layer_norm(pair.float(), (pair.shape[-1],), ln_w.float(), ln_b.float(), eps)
-    bias = F.linear(x, w_bias.float()).permute(2, 0, 1)
+    x, bias = pair_bias_fp32(pair, ln_w, ln_b, w_bias, eps)
     if transpose:
         x = x.permute(1, 0, 2)
     R, N, C = x.shape

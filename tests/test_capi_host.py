@@ -157,3 +157,16 @@ def test_pad_helpers():
     assert y.shape == (4, 4) and torch.equal(y[:2, :3], x) and y[3, 3] == 1.0
     z = A.pad_to_size(x, 5, 0)
     assert z.shape == (5, 3) and z[2:].abs().sum() == 0
+
+
+def test_pair_bias_argument_validation_codes():
+    lib = _capi.load()
+    one = ctypes.c_void_p(16)
+    args = lambda dtype=0, R=4, N=8, C=128, H=4, pitch=8: (one, dtype, R, N, C, H, one, one, one,
+                                                           ctypes.c_float(1e-5), one, one, pitch, None)
+    assert lib.af3k_pair_bias(*args(dtype=2)) == 1          # fp8 pair
+    assert lib.af3k_pair_bias(*args(C=64)) == 2             # only c_pair = 128
+    assert lib.af3k_pair_bias(*args(H=17)) == 2
+    assert lib.af3k_pair_bias(*args(pitch=7)) == 3          # pitch < N
+    assert lib.af3k_pair_bias(*args(N=8, pitch=12)) == 3    # pitch not a multiple of 8
+    assert lib.af3k_pair_bias(*args(R=0)) == 0              # empty problem
