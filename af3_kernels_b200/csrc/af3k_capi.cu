@@ -522,9 +522,9 @@ int af3k_pair_bias(const void* pair, int32_t pair_dtype, int64_t R, int64_t N, i
   p.pair = pair; p.normed = static_cast<__nv_bfloat16*>(normed); p.bias = static_cast<__nv_bfloat16*>(bias);
   p.gamma = gamma; p.beta = beta; p.proj = proj;
   p.R = (int)R; p.N = (int)N; p.H = (int)H; p.bias_pitch = bias_pitch; p.eps = eps;
-  // persistent CTAs, one per SM, over R * ceil(N / 128) tiles
+  // persistent CTAs (two per SM for the 4-head kernel, one for the wide ones) over R * ceil(N / 128) tiles
   const long long n_tiles = R * ((N + kPbTileJ - 1) / kPbTileJ);
-  const long long max_ctas = dev->sm_count;
+  const long long max_ctas = (long long)dev->sm_count * (H <= 4 ? 2 : 1);
   const unsigned grid = (unsigned)(n_tiles < max_ctas ? n_tiles : max_ctas);
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   const bool f32 = pair_dtype == AF3K_F32;

@@ -193,26 +193,23 @@ __device__ __forceinline__ float octet_sum(float v) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kPbThreads, 1) pair_bias_kernel_h4(const PairBiasParams p) {
+__global__ void __launch_bounds__(kPbThreads, 2) pair_bias_kernel_h4(const PairBiasParams p) {
   __shared__ __nv_bfloat16 s_bias[4][kPbTileJ];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grp = lane >> 3, sl = lane & 7;          // vector within the warp's four, lane within the vector
   // this lane's channels: [ca, ca + 8) and [cb, cb + 8)
   const int ca = sl * 8, cb = 64 + sl * 8;
 
-  float g[16], b[16], w[4][16];
+  // LayerNorm parameters and projection weights live in shared memory (3 KB): held in registers
+  // they cost 96 per thread, which left too few resident warps to cover the latencies
+  __shared__ __align__(16) float s_g[kPbChannels], s_b[kPbChannels], s_w[4][kPbChannels];
+  for (int c = threadIdx.x; c < kPbChannels; c += kPbThreads) {
+    s_g[c] = p.gamma[c];
+    s_b[c] = p.beta[c];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    g[e] = p.gamma[ca + e]; g[8 + e] = p.gamma[cb + e];
-    b[e] = p.beta[ca + e];  b[8 + e] = p.beta[cb + e];
+    for (int h = 0; h < 4; ++h) s_w[h][c] = h < p.H ? p.proj[h * kPbChannels + c] : 0.f;
   }
-#pragma unroll
-  for (int h = 0; h < 4; ++h)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      w[h][e] = h < p.H ? p.proj[h * kPbChannels + ca + e] : 0.f;
-      w[h][8 + e] = h < p.H ? p.proj[h * kPbChannels + cb + e] : 0.f;
-    }
+  __syncthreads();
 
   constexpr int kWarps = kPbThreads / 32;
   const int tiles_j = (p.N + kPbTileJ - 1) / kPbTileJ;
@@ -224,7 +221,7 @@ __global__ void __launch_bounds__(kPbThreads, 1) pair_bias_kernel_h4(const PairB
   // The warp's four passes over the tile: the raw loads of kDepth passes are issued before the
   // first is worked on, so that enough bytes are in flight per SM to cover the HBM latency.
   constexpr int kPasses = kPbTileJ / (kWarps * 4);
-  constexpr int kDepth = sizeof(T) == 2 ? 4 : 2;
+  constexpr int kDepth = 2;
   static_assert(kPasses % kDepth == 0, "passes per tile must be a multiple of the prefetch depth");
 #pragma unroll 1
   for (int pass0 = 0; pass0 < kPasses; pass0 += kDepth) {
@@ -286,8 +283,13 @@ __global__ void __launch_bounds__(kPbThreads, 1) pair_bias_kernel_h4(const PairB
     // values, the operand of the bias projection
     uint32_t yw[8];
 #pragma unroll
-    for (int e = 0; e < 8; ++e)
-      yw[e] = pb_pack_bf16x2(x[2 * e] * rstd * g[2 * e] + b[2 * e], x[2 * e + 1] * rstd * g[2 * e + 1] + b[2 * e + 1]);
+    for (int q4 = 0; q4 < 4; ++q4) {       // four channels at a time: x[4 q4 ..] are channels cq ..
+      const int cq = (q4 < 2 ? ca : cb) + 4 * (q4 & 1);
+      const float4 g4 = *reinterpret_cast<const float4*>(&s_g[cq]);
+      const float4 b4 = *reinterpret_cast<const float4*>(&s_b[cq]);
+      yw[2 * q4] = pb_pack_bf16x2(x[4 * q4] * rstd * g4.x + b4.x, x[4 * q4 + 1] * rstd * g4.y + b4.y);
+      yw[2 * q4 + 1] = pb_pack_bf16x2(x[4 * q4 + 2] * rstd * g4.z + b4.z, x[4 * q4 + 3] * rstd * g4.w + b4.w);
+    }
     if (live) {
       __nv_bfloat16* dst = p.normed + (row_base + j) * kPbChannels;
       *reinterpret_cast<uint4*>(dst + ca) = make_uint4(yw[0], yw[1], yw[2], yw[3]);
@@ -295,10 +297,15 @@ __global__ void __launch_bounds__(kPbThreads, 1) pair_bias_kernel_h4(const PairB
     }
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const float y0 = __uint_as_float(yw[e] << 16), y1 = __uint_as_float(yw[e] & 0xffff0000u);
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const int cq = (q4 < 2 ? ca : cb) + 4 * (q4 & 1);
+      const float y0 = __uint_as_float(yw[2 * q4] << 16), y1 = __uint_as_float(yw[2 * q4] & 0xffff0000u);
+      const float y2 = __uint_as_float(yw[2 * q4 + 1] << 16), y3 = __uint_as_float(yw[2 * q4 + 1] & 0xffff0000u);
 #pragma unroll
-      for (int h = 0; h < 4; ++h) acc[h] = fmaf(y1, w[h][2 * e + 1], fmaf(y0, w[h][2 * e], acc[h]));
+      for (int h = 0; h < 4; ++h) {
+        const float4 w4 = *reinterpret_cast<const float4*>(&s_w[h][cq]);
+        acc[h] = fmaf(y3, w4.w, fmaf(y2, w4.z, fmaf(y1, w4.y, fmaf(y0, w4.x, acc[h]))));
+      }
     }
     octet_sum_scatter<4>(acc, lane);
     // lanes 0, 2, 4, 6 of the octet hold heads 0, 1, 2, 3
