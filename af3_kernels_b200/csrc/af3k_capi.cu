@@ -93,6 +93,10 @@ int device_info(DeviceInfo** out) {
         (e = cudaFuncSetAttribute(attention_kernel<true, false>, attr, dyn)) != cudaSuccess ||
         (e = cudaFuncSetAttribute(attention_kernel<true, true>, attr, dyn)) != cudaSuccess)
       return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize)", e);
+    if ((e = cudaFuncSetAttribute(pair_bias_kernel_t<float>, attr, PbTile<float>::kSmemBytes)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(pair_bias_kernel_t<__nv_bfloat16>, attr, PbTile<__nv_bfloat16>::kSmemBytes)) !=
+            cudaSuccess)
+      return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize, pair_bias)", e);
     d.attr_set = true;
   }
   *out = &d;
@@ -529,8 +533,13 @@ int af3k_pair_bias(const void* pair, int32_t pair_dtype, int64_t R, int64_t N, i
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   const bool f32 = pair_dtype == AF3K_F32;
   if (H <= 4) {
-    if (f32) pair_bias_kernel_h4<float><<<grid, kPbThreads, 0, stream>>>(p);
-    else     pair_bias_kernel_h4<__nv_bfloat16><<<grid, kPbThreads, 0, stream>>>(p);
+    // one thread per vector, tiles transposed through shared memory; five CTAs fit an SM
+    const long long tiles_t = R * ((N + (f32 ? 64 : 128) - 1) / (f32 ? 64 : 128));
+    const long long cap = (long long)dev->sm_count * 5;
+    const unsigned grid_t = (unsigned)(tiles_t < cap ? tiles_t : cap);
+    if (f32) pair_bias_kernel_t<float><<<grid_t, PbTile<float>::kRows, PbTile<float>::kSmemBytes, stream>>>(p);
+    else     pair_bias_kernel_t<__nv_bfloat16><<<grid_t, PbTile<__nv_bfloat16>::kRows,
+                                                PbTile<__nv_bfloat16>::kSmemBytes, stream>>>(p);
   } else if (H <= 8) {
     if (f32) pair_bias_kernel<float, 8><<<grid, kPbThreads, 0, stream>>>(p);
     else     pair_bias_kernel<__nv_bfloat16, 8><<<grid, kPbThreads, 0, stream>>>(p);

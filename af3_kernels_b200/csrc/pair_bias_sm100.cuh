@@ -10,11 +10,12 @@
 // pair (bf16, the operand of the q / k / v / gate projections) and the bias (bf16, [H, N, N],
 // rows 16-byte aligned so that the attention kernel's TMA reads it in place) are written once.
 //
-// HBM-bound: 2 or 4 bytes read and 2 bytes written per pair element, plus H * 2 bytes per
-// (i, j).  One warp normalises one 128-channel vector (4 channels per lane, statistics by
-// shuffles in fp32; with up to four heads 8 lanes share a vector); persistent CTAs walk over tiles
-// of 128 consecutive j of one row i and stage each tile's H x 128 bias values in shared memory so
-// that they leave as 256-byte rows.
+// HBM traffic: 2 or 4 bytes read and 2 bytes written per pair element, plus H * 2 bytes per
+// (i, j).  Two kernels.  Up to four heads (the grid / triangle attention of AlphaFold3): one thread
+// per vector, tiles transposed through shared memory, no cross-lane reductions.  Five to sixteen
+// heads: one warp per vector (4 channels per lane, statistics by shuffles in fp32).  Both run as
+// persistent CTAs over tiles of consecutive j of one row i and stage each tile's bias values in
+// shared memory so that they leave as full 16-byte pieces.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -161,170 +162,147 @@ __global__ void __launch_bounds__(kPbThreads) pair_bias_kernel(const PairBiasPar
   }
 }
 
-// ---------------------------------------------------------------- up to 4 heads: 8 lanes per vector
-// The kernel above spends most of its instructions on 32-lane reductions (about 150 warp
-// instructions per vector against 44 of arithmetic), which makes it issue-bound at under half of
-// the HBM rate.  With at most four heads the weights of 16 channels fit a lane's registers, so
-// here 8 lanes share a vector (16 channels each, as two 16-byte pieces 128 bytes apart, so that
-// the 8 lanes of a load cover 128 contiguous bytes) and a warp works on 4 vectors at once:
-// reductions take 3 steps, and all control is amortised over 4 vectors.
-template <int kN>
-__device__ __forceinline__ void octet_sum_scatter(float (&a)[kN], int lane) {
-  static_assert(kN == 1 || kN == 2 || kN == 4, "power of two up to 4");
-  int off = 4;
+// ---------------------------------------------------------------- up to 4 heads: one thread per vector
+// The reductions are what held the kernels above back (chains of dependent shuffles), so here a
+// vector is not shared between lanes at all: a tile of vectors is copied to shared memory with
+// coalesced 16-byte loads (rows padded by 16 bytes, so that the 8 lanes of a 128-bit access
+// phase hit different banks), then thread t walks over row t twice (moments; normalise, round,
+// project), writes the bf16 result back over the row, and the
+// tile leaves again with coalesced stores.  The constants are read from shared memory as
+// warp-wide broadcasts.
+template <typename T>
+struct PbTile {
+  static constexpr int kRows = sizeof(T) == 2 ? 128 : 64;           // vectors per tile = threads per CTA
+  static constexpr int kRowBytes = kPbChannels * (int)sizeof(T);
+  static constexpr int kStride = kRowBytes + 16;                    // bytes between rows in shared memory
+  static constexpr int kPieces = kRowBytes / 16;                    // 16-byte pieces per row
+  static constexpr int kSmemBytes = kRows * kStride + 6 * kPbChannels * 4 + 4 * kRows * 2;
+};
+
+template <typename T>
+__device__ __forceinline__ void pb_unpack8(const uint4& v, const uint4& v2, float (&x)[8]) {
+  if (sizeof(T) == 4) {
+    x[0] = __uint_as_float(v.x); x[1] = __uint_as_float(v.y); x[2] = __uint_as_float(v.z); x[3] = __uint_as_float(v.w);
+    x[4] = __uint_as_float(v2.x); x[5] = __uint_as_float(v2.y); x[6] = __uint_as_float(v2.z); x[7] = __uint_as_float(v2.w);
+  } else {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-  for (int n = kN; n > 1; n >>= 1) {
-    const bool upper = (lane & off) != 0;
-#pragma unroll
-    for (int k = 0; k < n / 2; ++k) {
-      const float send = upper ? a[k] : a[k + n / 2];
-      const float keep = upper ? a[k + n / 2] : a[k];
-      a[k] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-    }
-    off >>= 1;
+    for (int e = 0; e < 4; ++e) { x[2 * e] = __uint_as_float(w[e] << 16); x[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
   }
-  for (; off > 0; off >>= 1) a[0] += __shfl_xor_sync(0xffffffffu, a[0], off);
-}
-__device__ __forceinline__ float octet_sum(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 4);
-  v += __shfl_xor_sync(0xffffffffu, v, 2);
-  v += __shfl_xor_sync(0xffffffffu, v, 1);
-  return v;
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kPbThreads, 2) pair_bias_kernel_h4(const PairBiasParams p) {
-  __shared__ __nv_bfloat16 s_bias[4][kPbTileJ];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int grp = lane >> 3, sl = lane & 7;          // vector within the warp's four, lane within the vector
-  // this lane's channels: [ca, ca + 8) and [cb, cb + 8)
-  const int ca = sl * 8, cb = 64 + sl * 8;
-
-  // LayerNorm parameters and projection weights live in shared memory (3 KB): held in registers
-  // they cost 96 per thread, which left too few resident warps to cover the latencies
-  __shared__ __align__(16) float s_g[kPbChannels], s_b[kPbChannels], s_w[4][kPbChannels];
-  for (int c = threadIdx.x; c < kPbChannels; c += kPbThreads) {
-    s_g[c] = p.gamma[c];
-    s_b[c] = p.beta[c];
+__global__ void __launch_bounds__(PbTile<T>::kRows, 512 / PbTile<T>::kRows) pair_bias_kernel_t(const PairBiasParams p) {
+  using Tl = PbTile<T>;
+  extern __shared__ __align__(16) uint8_t pb_smem[];
+  float* s_c = reinterpret_cast<float*>(pb_smem + Tl::kRows * Tl::kStride);   // g, b, w0..w3: [6][128]
+  __nv_bfloat16* s_bias = reinterpret_cast<__nv_bfloat16*>(s_c + 6 * kPbChannels);   // [4][kRows]
+  const int t = threadIdx.x;
+  for (int c = t; c < kPbChannels; c += Tl::kRows) {
+    s_c[c] = p.gamma[c];
+    s_c[kPbChannels + c] = p.beta[c];
 #pragma unroll
-    for (int h = 0; h < 4; ++h) s_w[h][c] = h < p.H ? p.proj[h * kPbChannels + c] : 0.f;
+    for (int h = 0; h < 4; ++h) s_c[(2 + h) * kPbChannels + c] = h < p.H ? p.proj[h * kPbChannels + c] : 0.f;
   }
-  __syncthreads();
-
-  constexpr int kWarps = kPbThreads / 32;
-  const int tiles_j = (p.N + kPbTileJ - 1) / kPbTileJ;
+  const int tiles_j = (p.N + Tl::kRows - 1) / Tl::kRows;
   const long long n_tiles = (long long)p.R * tiles_j;
-  for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {   // persistent: constants loaded once
-  const int i = (int)(tile / tiles_j);
-  const int j0 = (int)(tile % tiles_j) * kPbTileJ;
-  const long long row_base = (long long)i * p.N;
-  // The warp's four passes over the tile: the raw loads of kDepth passes are issued before the
-  // first is worked on, so that enough bytes are in flight per SM to cover the HBM latency.
-  constexpr int kPasses = kPbTileJ / (kWarps * 4);
-  constexpr int kDepth = 2;
-  static_assert(kPasses % kDepth == 0, "passes per tile must be a multiple of the prefetch depth");
-#pragma unroll 1
-  for (int pass0 = 0; pass0 < kPasses; pass0 += kDepth) {
-  uint4 raw[kDepth][sizeof(T) == 2 ? 2 : 4];
-#pragma unroll
-  for (int dpt = 0; dpt < kDepth; ++dpt) {
-    const int j = j0 + (pass0 + dpt) * kWarps * 4 + warp * 4 + grp;
-    if (j < p.N) {
-      const long long off = (row_base + j) * kPbChannels;
-      if (sizeof(T) == 4) {
-        const float* src = static_cast<const float*>(p.pair) + off;
-        raw[dpt][0] = *reinterpret_cast<const uint4*>(src + ca);
-        raw[dpt][1] = *reinterpret_cast<const uint4*>(src + ca + 4);
-        raw[dpt][2] = *reinterpret_cast<const uint4*>(src + cb);
-        raw[dpt][3] = *reinterpret_cast<const uint4*>(src + cb + 4);
-      } else {
-        const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.pair) + off;
-        raw[dpt][0] = *reinterpret_cast<const uint4*>(src + ca);
-        raw[dpt][1] = *reinterpret_cast<const uint4*>(src + cb);
-      }
-    } else {
-#pragma unroll
-      for (int r = 0; r < (sizeof(T) == 2 ? 2 : 4); ++r) raw[dpt][r] = make_uint4(0u, 0u, 0u, 0u);
+  // global -> shared, coalesced (the tile's vectors are contiguous in memory), as asynchronous
+  // 16-byte copies: the whole tile is in flight at once and no registers are held.  (A second
+  // row buffer that prefetches the next tile was slower: it costs two of the five resident CTAs.)
+  auto request_tile = [&](long long tile, uint8_t* buf) {
+    const int j0 = (int)(tile % tiles_j) * Tl::kRows;
+    const int rows = min(Tl::kRows, p.N - j0);
+    const long long vec0 = (tile / tiles_j) * p.N + j0;
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.pair) + vec0 * Tl::kRowBytes);
+    for (int k = t; k < rows * Tl::kPieces; k += Tl::kRows) {
+      const uint32_t dst_s = (uint32_t)__cvta_generic_to_shared(buf + (k / Tl::kPieces) * Tl::kStride +
+                                                                (k % Tl::kPieces) * 16);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_s), "l"(src + k) : "memory");
     }
-  }
-#pragma unroll
-  for (int dpt = 0; dpt < kDepth; ++dpt) {
-    const int jl = (pass0 + dpt) * kWarps * 4 + warp * 4 + grp;   // vector within the CTA's tile
-    const int j = j0 + jl;
-    const bool live = j < p.N;
-    float x[16];
-    if (sizeof(T) == 4) {
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        x[4 * r + 0] = __uint_as_float(raw[dpt][r].x); x[4 * r + 1] = __uint_as_float(raw[dpt][r].y);
-        x[4 * r + 2] = __uint_as_float(raw[dpt][r].z); x[4 * r + 3] = __uint_as_float(raw[dpt][r].w);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  uint8_t* s_rows = pb_smem;
+  for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int i = (int)(tile / tiles_j);
+    const int j0 = (int)(tile % tiles_j) * Tl::kRows;
+    const int rows = min(Tl::kRows, p.N - j0);
+    const long long vec0 = (long long)i * p.N + j0;                 // first vector of the tile
+    request_tile(tile, s_rows);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (t < rows) {
+      const uint8_t* row = s_rows + t * Tl::kStride;
+      constexpr int kStep = sizeof(T) == 2 ? 16 : 32;               // bytes per 8 channels
+      // mean and (biased) variance in one walk over the row, as moments about the row's first
+      // element (a sample of the distribution, so the subtraction of the squared mean loses at
+      // most a bit or two)
+      float pivot;
+      {
+        float x[8];
+        pb_unpack8<T>(*reinterpret_cast<const uint4*>(row), *reinterpret_cast<const uint4*>(row + (sizeof(T) == 2 ? 0 : 16)), x);
+        pivot = x[0];
       }
-    } else {
+      float s1a = 0.f, s1b = 0.f, s2a = 0.f, s2b = 0.f;
+#pragma unroll 2
+      for (int c8 = 0; c8 < kPbChannels / 8; ++c8) {
+        float x[8];
+        pb_unpack8<T>(*reinterpret_cast<const uint4*>(row + c8 * kStep),
+                      *reinterpret_cast<const uint4*>(row + c8 * kStep + (sizeof(T) == 2 ? 0 : 16)), x);
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const uint32_t ww[4] = {raw[dpt][r].x, raw[dpt][r].y, raw[dpt][r].z, raw[dpt][r].w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          x[8 * r + 2 * e] = __uint_as_float(ww[e] << 16);
-          x[8 * r + 2 * e + 1] = __uint_as_float(ww[e] & 0xffff0000u);
+        for (int e = 0; e < 8; e += 2) {
+          const float d0 = x[e] - pivot, d1 = x[e + 1] - pivot;
+          s1a += d0; s1b += d1;
+          s2a = fmaf(d0, d0, s2a); s2b = fmaf(d1, d1, s2b);
         }
       }
+      const float m1 = (s1a + s1b) * (1.0f / kPbChannels);
+      const float mean = pivot + m1;
+      const float var = fmaxf((s2a + s2b) * (1.0f / kPbChannels) - m1 * m1, 0.f);
+      const float rstd = rsqrtf(var + p.eps);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+      for (int c8 = 0; c8 < kPbChannels / 8; ++c8) {
+        float x[8];
+        pb_unpack8<T>(*reinterpret_cast<const uint4*>(row + c8 * kStep),
+                      *reinterpret_cast<const uint4*>(row + c8 * kStep + (sizeof(T) == 2 ? 0 : 16)), x);
+        uint32_t yw[4];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const float4 g4 = *reinterpret_cast<const float4*>(&s_c[c8 * 8 + 4 * q]);
+          const float4 b4 = *reinterpret_cast<const float4*>(&s_c[kPbChannels + c8 * 8 + 4 * q]);
+          yw[2 * q] = pb_pack_bf16x2((x[4 * q] - mean) * rstd * g4.x + b4.x, (x[4 * q + 1] - mean) * rstd * g4.y + b4.y);
+          yw[2 * q + 1] = pb_pack_bf16x2((x[4 * q + 2] - mean) * rstd * g4.z + b4.z, (x[4 * q + 3] - mean) * rstd * g4.w + b4.w);
+          const float y0 = __uint_as_float(yw[2 * q] << 16), y1 = __uint_as_float(yw[2 * q] & 0xffff0000u);
+          const float y2 = __uint_as_float(yw[2 * q + 1] << 16), y3 = __uint_as_float(yw[2 * q + 1] & 0xffff0000u);
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            const float4 w4 = *reinterpret_cast<const float4*>(&s_c[(2 + h) * kPbChannels + c8 * 8 + 4 * q]);
+            acc[h] = fmaf(y3, w4.w, fmaf(y2, w4.z, fmaf(y1, w4.y, fmaf(y0, w4.x, acc[h]))));
+          }
+        }
+        // the bf16 result goes back over the part of the row that has been consumed
+        *reinterpret_cast<uint4*>(s_rows + t * Tl::kStride + c8 * 16) = make_uint4(yw[0], yw[1], yw[2], yw[3]);
+      }
+#pragma unroll
+      for (int h = 0; h < 4; ++h) s_bias[h * Tl::kRows + t] = __float2bfloat16_rn(acc[h]);
     }
-    // mean and (biased) variance over the 128 channels, two-pass in registers
-    float sum = 0.f;
-#pragma unroll
-    for (int e = 0; e < 16; ++e) sum += x[e];
-    const float mean = octet_sum(sum) * (1.0f / kPbChannels);
-    float sq = 0.f;
-#pragma unroll
-    for (int e = 0; e < 16; ++e) { x[e] -= mean; sq += x[e] * x[e]; }
-    const float rstd = rsqrtf(octet_sum(sq) * (1.0f / kPbChannels) + p.eps);
-    // y = bf16(d * rstd * gamma + beta): written as the normalised pair and, as those same rounded
-    // values, the operand of the bias projection
-    uint32_t yw[8];
-#pragma unroll
-    for (int q4 = 0; q4 < 4; ++q4) {       // four channels at a time: x[4 q4 ..] are channels cq ..
-      const int cq = (q4 < 2 ? ca : cb) + 4 * (q4 & 1);
-      const float4 g4 = *reinterpret_cast<const float4*>(&s_g[cq]);
-      const float4 b4 = *reinterpret_cast<const float4*>(&s_b[cq]);
-      yw[2 * q4] = pb_pack_bf16x2(x[4 * q4] * rstd * g4.x + b4.x, x[4 * q4 + 1] * rstd * g4.y + b4.y);
-      yw[2 * q4 + 1] = pb_pack_bf16x2(x[4 * q4 + 2] * rstd * g4.z + b4.z, x[4 * q4 + 3] * rstd * g4.w + b4.w);
-    }
-    if (live) {
-      __nv_bfloat16* dst = p.normed + (row_base + j) * kPbChannels;
-      *reinterpret_cast<uint4*>(dst + ca) = make_uint4(yw[0], yw[1], yw[2], yw[3]);
-      *reinterpret_cast<uint4*>(dst + cb) = make_uint4(yw[4], yw[5], yw[6], yw[7]);
-    }
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int q4 = 0; q4 < 4; ++q4) {
-      const int cq = (q4 < 2 ? ca : cb) + 4 * (q4 & 1);
-      const float y0 = __uint_as_float(yw[2 * q4] << 16), y1 = __uint_as_float(yw[2 * q4] & 0xffff0000u);
-      const float y2 = __uint_as_float(yw[2 * q4 + 1] << 16), y3 = __uint_as_float(yw[2 * q4 + 1] & 0xffff0000u);
-#pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        const float4 w4 = *reinterpret_cast<const float4*>(&s_w[h][cq]);
-        acc[h] = fmaf(y3, w4.w, fmaf(y2, w4.z, fmaf(y1, w4.y, fmaf(y0, w4.x, acc[h]))));
+    __syncthreads();
+    // ---- shared -> global, coalesced: normalised rows (256 bytes each), then the bias rows
+    uint4* dst = reinterpret_cast<uint4*>(p.normed + vec0 * kPbChannels);
+#pragma unroll 4
+    for (int k = t; k < rows * 16; k += Tl::kRows)
+      dst[k] = *reinterpret_cast<const uint4*>(s_rows + (k / 16) * Tl::kStride + (k % 16) * 16);
+    for (int k = t; k < p.H * (Tl::kRows / 8); k += Tl::kRows) {
+      const int h = k / (Tl::kRows / 8), seg = k % (Tl::kRows / 8);
+      const int j = j0 + seg * 8;
+      __nv_bfloat16* bd = p.bias + ((long long)h * p.R + i) * p.bias_pitch + j;
+      if (j + 8 <= p.N) {
+        *reinterpret_cast<uint4*>(bd) = *reinterpret_cast<const uint4*>(&s_bias[h * Tl::kRows + seg * 8]);
+      } else {
+        for (int e = 0; e < 8 && j + e < p.N; ++e) bd[e] = s_bias[h * Tl::kRows + seg * 8 + e];
       }
     }
-    octet_sum_scatter<4>(acc, lane);
-    // lanes 0, 2, 4, 6 of the octet hold heads 0, 1, 2, 3
-    if ((sl & 1) == 0) s_bias[sl >> 1][jl] = __float2bfloat16_rn(acc[0]);
-  }
-  }
-  __syncthreads();
-  // H rows of 128 bf16 = 256 bytes each: 16 threads x 16 bytes per head
-  const int h = threadIdx.x >> 4, seg = threadIdx.x & 15;
-  if (h < p.H) {
-    const int j = j0 + seg * 8;
-    __nv_bfloat16* dst = p.bias + ((long long)h * p.R + i) * p.bias_pitch + j;
-    if (j + 8 <= p.N) {
-      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&s_bias[h][seg * 8]);
-    } else {
-      for (int e = 0; e < 8 && j + e < p.N; ++e) dst[e] = s_bias[h][seg * 8 + e];
-    }
-  }
-  __syncthreads();   // s_bias is reused by the next tile
+    __syncthreads();   // the row buffer and s_bias are reused by the next tile
   }
 }
 

@@ -466,7 +466,7 @@ def pair_bias_line(args, dev):
                       "warmup": max(args.warmup, 3), "ms_per_step": ms,
                       "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                    "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                                   "kernel": "pair_bias_kernel", "algorithmic_bytes_per_launch": alg_bytes,
+                                   "kernel": "pair_bias_kernel_t", "algorithmic_bytes_per_launch": alg_bytes,
                                    "traffic": None},
                       "config": {"workload": f"pair-bias producer, pair [{N},{N},{C}] bf16 -> normed bf16 + bias [{H},{N},{N}] bf16",
                                  "cache": "three buffer sets in rotation (920 MB > L2)"},
