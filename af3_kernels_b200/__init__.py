@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 
 from . import _capi
-from .dpa import dot_product_attention, read_status
+from .dpa import dot_product_attention, dot_product_attention_host, read_status
 from .tools import pad_to_size, print_comm_time, profile, record_comm_time
 from .distributed import RowShardedAttention, row_partition
 from .fused_ops import attention_block, self_attention_block
@@ -21,6 +21,7 @@ from .Attention import GridSelfAttentionCpp, DistributedGridSelfAttentionCpp
 __all__ = [
     "dot_product_attention_cpp",
     "dot_product_attention",
+    "dot_product_attention_host",
     "RowShardedAttention",
     "row_partition",
     "GridSelfAttentionCpp",
@@ -57,10 +58,16 @@ def dot_product_attention_cpp(
     ``use_flash_attention``, ``BLK_SZ`` and ``FLASH_SZ`` are accepted and checked but do not
     select code: the CUDA kernel always runs an online softmax over 128-key tiles.  Unlike the
     reference the call never writes to ``q`` and a 1-D mask broadcasts over the batch.
-    ``q_scale`` / ``k_scale`` (keyword-only) enable float8_e4m3fn q and k.
+    ``q_scale`` / ``k_scale`` (keyword-only) enable float8_e4m3fn q and k.  CUDA tensors are
+    computed in place on their device; host tensors (what the reference takes) go through
+    ``dot_product_attention_host`` and come back as a host tensor.
     """
     if int(BLK_SZ) <= 0 or int(FLASH_SZ) <= 0:
         raise ValueError("BLK_SZ and FLASH_SZ must be positive")
+    if not q.is_cuda:
+        # host tensors, as the reference takes them: pipelined over PCIe, computed on the GPU,
+        # result in host memory
+        return dot_product_attention_host(q, k, v, mask, bias, q_scale=q_scale, k_scale=k_scale)
     return dot_product_attention(q, k, v, mask, bias, q_scale=q_scale, k_scale=k_scale)
 
 

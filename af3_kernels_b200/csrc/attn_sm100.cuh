@@ -57,7 +57,7 @@ constexpr int kTile = 128;         // query rows per tile == keys per tile
 constexpr int kThreads = 384;      // 12 warps
 // 65536 registers per SM: launched at 168 per thread, then 128 x 56 + 256 x 224 = 64512
 constexpr int kRegsMisc = 56, kRegsSoftmax = 224;
-constexpr int kMaxStreams = 4;     // pair rows per work item (TMEM: kOCol + G * nv <= 512 columns)
+constexpr int kMaxStreams = 4;     // pair rows per work item (two per softmax warpgroup; TMEM: kOCol + G * nv <= 512 columns)
 // TMEM columns: two fp32 logits buffers, two bf16 P buffers (two keys per column), then O.
 constexpr uint32_t kSCol = 0, kPCol = 2 * 128, kOCol = 2 * 128 + 2 * 64;
 constexpr float kLazyRescaleLog2 = 8.0f;   // keep a stale row max while exp2 arguments stay <= 8
@@ -125,7 +125,7 @@ struct BarIdx {
   // Q tiles: slot = (Q buffer) * kMaxStreams + stream
   static constexpr int q_full = 12 + 2 * kMaxKvStages;       // [2 * kMaxStreams]  Q tile landed
   static constexpr int q_empty = q_full + 2 * kMaxStreams;   // [2 * kMaxStreams]  last Q K^T of the stream finished
-  static constexpr int q_scaled = q_empty + 2 * kMaxStreams; // [2 * kMaxStreams]  warp 3 has scaled the Q tile
+  static constexpr int q_scaled = q_empty + 2 * kMaxStreams; // [2 * kMaxStreams]  the P V warp has scaled the Q tile
   static constexpr int count = q_scaled + 2 * kMaxStreams;
 };
 static_assert(BarIdx::count * 8 <= (int)kBarrierBlockBytes, "barrier block too small");

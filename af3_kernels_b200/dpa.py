@@ -175,3 +175,93 @@ def dot_product_attention(
                     f"block {st[2]}, warp {st[3]})"
                 )
     return out
+
+
+def dot_product_attention_host(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    mask: Optional[torch.Tensor],
+    bias: torch.Tensor,
+    *,
+    q_scale: Optional[torch.Tensor] = None,
+    k_scale: Optional[torch.Tensor] = None,
+    softmax_scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+    device: Optional[torch.device] = None,
+    chunks: int = 8,
+) -> torch.Tensor:
+    """The same operator for HOST tensors (what a caller of the reference, a CPU library, holds):
+    q, k, v ``[B1, B2, S, D]`` in host memory, result in host memory.
+
+    The batch rows are independent problems, so the call is a three-stage pipeline over ``chunks``
+    row blocks on three CUDA streams: host-to-device copies of block *i + 1*, the kernel on block
+    *i* and the device-to-host copy of block *i - 1* run at the same time (PCIe is full duplex), so
+    the call costs about the time of the larger transfer instead of the sum of all three.  Bias and
+    mask go over once.  Pinned host tensors (``tensor.pin_memory()``) are what makes the copies
+    asynchronous; pageable ones work but serialise.  ``out`` may be a preallocated (pinned) host
+    tensor.  The call returns after the result has arrived in host memory.
+    """
+    if q.is_cuda or k.is_cuda or v.is_cuda:
+        raise ValueError("dot_product_attention_host takes host tensors; use dot_product_attention for CUDA ones")
+    if not torch.cuda.is_available():
+        raise RuntimeError("af3_kernels_b200 needs a CUDA device (there is no CPU fallback)")
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    if q.dim() != 4:
+        raise ValueError("q, k, v must be 4-D [B1, B2, S, D]")
+    B1, B2, Sq, D = q.shape
+    if out is None:
+        out = torch.empty((B1, B2, Sq, D), dtype=torch.bfloat16, pin_memory=True)
+    elif out.is_cuda or out.shape != (B1, B2, Sq, D) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bf16 host tensor [B1, B2, Sq, D]")
+    if B1 == 0 or out.numel() == 0:
+        return out
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    n_chunks = max(1, min(int(chunks), B1))
+    bounds = [B1 * i // n_chunks for i in range(n_chunks + 1)]
+
+    with torch.cuda.device(dev):
+        main = torch.cuda.current_stream()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        s_in.wait_stream(main)
+        s_out.wait_stream(main)
+        # bias and mask once; an fp32 bias is rounded to bf16 here instead of once per row block
+        bias_d = bias.to(dev, non_blocking=True)
+        if bias_d.dtype not in (torch.bfloat16,):
+            bias_d = bias_d.to(torch.bfloat16)
+        mask_d = None if mask is None else mask.to(dev, non_blocking=True)
+        qs = None if q_scale is None else q_scale.to(dev, non_blocking=True)
+        ks = None if k_scale is None else k_scale.to(dev, non_blocking=True)
+        per_row_mask = mask_d is not None and mask_d.dim() >= 2 and mask_d.reshape(-1, mask_d.shape[-1]).shape[0] == B1 \
+            and B1 != 1
+        if per_row_mask:
+            mask_d = mask_d.reshape(B1, mask_d.shape[-1])
+        dq = torch.empty(q.shape, dtype=q.dtype, device=dev)
+        dk = torch.empty(k.shape, dtype=k.dtype, device=dev)
+        dv = torch.empty(v.shape, dtype=v.dtype, device=dev)
+        do = torch.empty((B1, B2, Sq, D), dtype=torch.bfloat16, device=dev)
+        for i in range(n_chunks):
+            lo, hi = bounds[i], bounds[i + 1]
+            if lo == hi:
+                continue
+            with torch.cuda.stream(s_in):
+                dq[lo:hi].copy_(q[lo:hi], non_blocking=True)
+                dk[lo:hi].copy_(k[lo:hi], non_blocking=True)
+                dv[lo:hi].copy_(v[lo:hi], non_blocking=True)
+                landed = torch.cuda.Event()
+                landed.record(s_in)
+            main.wait_event(landed)
+            dot_product_attention(dq[lo:hi], dk[lo:hi], dv[lo:hi],
+                                  mask_d[lo:hi] if per_row_mask else mask_d, bias_d,
+                                  q_scale=qs, k_scale=ks, softmax_scale=softmax_scale, out=do[lo:hi])
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                out[lo:hi].copy_(do[lo:hi], non_blocking=True)
+        main.wait_stream(s_out)
+        for t in (dq, dk, dv, do):
+            t.record_stream(s_in)
+            t.record_stream(s_out)
+        s_out.synchronize()
+    return out
