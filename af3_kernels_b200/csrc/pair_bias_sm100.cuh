@@ -21,6 +21,8 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
+#include "ptx_sm100.cuh"
+
 namespace af3k {
 
 constexpr int kPbChannels = 128;   // c_pair
@@ -192,7 +194,7 @@ __device__ __forceinline__ void pb_unpack8(const uint4& v, const uint4& v2, floa
 }
 
 template <typename T>
-__global__ void __launch_bounds__(PbTile<T>::kRows, 512 / PbTile<T>::kRows) pair_bias_kernel_t(const PairBiasParams p) {
+__global__ void __launch_bounds__(PbTile<T>::kRows, 640 / PbTile<T>::kRows) pair_bias_kernel_t(const PairBiasParams p) {
   using Tl = PbTile<T>;
   extern __shared__ __align__(16) uint8_t pb_smem[];
   float* s_c = reinterpret_cast<float*>(pb_smem + Tl::kRows * Tl::kStride);   // g, b, w0..w3: [6][128]
@@ -242,24 +244,34 @@ __global__ void __launch_bounds__(PbTile<T>::kRows, 512 / PbTile<T>::kRows) pair
         pb_unpack8<T>(*reinterpret_cast<const uint4*>(row), *reinterpret_cast<const uint4*>(row + (sizeof(T) == 2 ? 0 : 16)), x);
         pivot = x[0];
       }
-      float s1a = 0.f, s1b = 0.f, s2a = 0.f, s2b = 0.f;
+      const uint64_t npivot2 = pack_f32x2(-pivot, -pivot);
+      uint64_t s1a = pack_f32x2(0.f, 0.f), s1b = s1a, s2a = s1a, s2b = s1a;
 #pragma unroll 2
       for (int c8 = 0; c8 < kPbChannels / 8; ++c8) {
         float x[8];
         pb_unpack8<T>(*reinterpret_cast<const uint4*>(row + c8 * kStep),
                       *reinterpret_cast<const uint4*>(row + c8 * kStep + (sizeof(T) == 2 ? 0 : 16)), x);
+        // packed f32x2 arithmetic: two channels per FMA-pipe instruction
 #pragma unroll
-        for (int e = 0; e < 8; e += 2) {
-          const float d0 = x[e] - pivot, d1 = x[e + 1] - pivot;
-          s1a += d0; s1b += d1;
-          s2a = fmaf(d0, d0, s2a); s2b = fmaf(d1, d1, s2b);
+        for (int e = 0; e < 8; e += 4) {
+          const uint64_t da = add_f32x2(pack_f32x2(x[e], x[e + 1]), npivot2);
+          const uint64_t db = add_f32x2(pack_f32x2(x[e + 2], x[e + 3]), npivot2);
+          s1a = add_f32x2(s1a, da); s1b = add_f32x2(s1b, db);
+          s2a = fma_f32x2(da, da, s2a); s2b = fma_f32x2(db, db, s2b);
         }
       }
-      const float m1 = (s1a + s1b) * (1.0f / kPbChannels);
+      float s1lo, s1hi, s2lo, s2hi;
+      unpack_f32x2(add_f32x2(s1a, s1b), s1lo, s1hi);
+      unpack_f32x2(add_f32x2(s2a, s2b), s2lo, s2hi);
+      const float m1 = (s1lo + s1hi) * (1.0f / kPbChannels);
       const float mean = pivot + m1;
-      const float var = fmaxf((s2a + s2b) * (1.0f / kPbChannels) - m1 * m1, 0.f);
+      const float var = fmaxf((s2lo + s2hi) * (1.0f / kPbChannels) - m1 * m1, 0.f);
       const float rstd = rsqrtf(var + p.eps);
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      // y = x * A + B per channel with A = rstd * gamma, B = beta - mean * A
+      const uint64_t rstd2 = pack_f32x2(rstd, rstd), nmean2 = pack_f32x2(-mean, -mean);
+      uint64_t acc2[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) acc2[h] = pack_f32x2(0.f, 0.f);
 #pragma unroll 2
       for (int c8 = 0; c8 < kPbChannels / 8; ++c8) {
         float x[8];
@@ -268,20 +280,34 @@ __global__ void __launch_bounds__(PbTile<T>::kRows, 512 / PbTile<T>::kRows) pair
         uint32_t yw[4];
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
-          const float4 g4 = *reinterpret_cast<const float4*>(&s_c[c8 * 8 + 4 * q]);
-          const float4 b4 = *reinterpret_cast<const float4*>(&s_c[kPbChannels + c8 * 8 + 4 * q]);
-          yw[2 * q] = pb_pack_bf16x2((x[4 * q] - mean) * rstd * g4.x + b4.x, (x[4 * q + 1] - mean) * rstd * g4.y + b4.y);
-          yw[2 * q + 1] = pb_pack_bf16x2((x[4 * q + 2] - mean) * rstd * g4.z + b4.z, (x[4 * q + 3] - mean) * rstd * g4.w + b4.w);
-          const float y0 = __uint_as_float(yw[2 * q] << 16), y1 = __uint_as_float(yw[2 * q] & 0xffff0000u);
-          const float y2 = __uint_as_float(yw[2 * q + 1] << 16), y3 = __uint_as_float(yw[2 * q + 1] & 0xffff0000u);
+          const ulonglong2 g4 = *reinterpret_cast<const ulonglong2*>(&s_c[c8 * 8 + 4 * q]);
+          const ulonglong2 b4 = *reinterpret_cast<const ulonglong2*>(&s_c[kPbChannels + c8 * 8 + 4 * q]);
+          const uint64_t a01 = mul_f32x2(g4.x, rstd2), a23 = mul_f32x2(g4.y, rstd2);
+          const uint64_t y01 = fma_f32x2(pack_f32x2(x[4 * q], x[4 * q + 1]), a01, fma_f32x2(a01, nmean2, b4.x));
+          const uint64_t y23 = fma_f32x2(pack_f32x2(x[4 * q + 2], x[4 * q + 3]), a23, fma_f32x2(a23, nmean2, b4.y));
+          float y0, y1, y2, y3;
+          unpack_f32x2(y01, y0, y1);
+          unpack_f32x2(y23, y2, y3);
+          yw[2 * q] = pb_pack_bf16x2(y0, y1);
+          yw[2 * q + 1] = pb_pack_bf16x2(y2, y3);
+          // the projection sees the rounded values
+          const uint64_t r01 = pack_f32x2(__uint_as_float(yw[2 * q] << 16), __uint_as_float(yw[2 * q] & 0xffff0000u));
+          const uint64_t r23 = pack_f32x2(__uint_as_float(yw[2 * q + 1] << 16), __uint_as_float(yw[2 * q + 1] & 0xffff0000u));
 #pragma unroll
           for (int h = 0; h < 4; ++h) {
-            const float4 w4 = *reinterpret_cast<const float4*>(&s_c[(2 + h) * kPbChannels + c8 * 8 + 4 * q]);
-            acc[h] = fmaf(y3, w4.w, fmaf(y2, w4.z, fmaf(y1, w4.y, fmaf(y0, w4.x, acc[h]))));
+            const ulonglong2 w4 = *reinterpret_cast<const ulonglong2*>(&s_c[(2 + h) * kPbChannels + c8 * 8 + 4 * q]);
+            acc2[h] = fma_f32x2(r23, w4.y, fma_f32x2(r01, w4.x, acc2[h]));
           }
         }
         // the bf16 result goes back over the part of the row that has been consumed
         *reinterpret_cast<uint4*>(s_rows + t * Tl::kStride + c8 * 16) = make_uint4(yw[0], yw[1], yw[2], yw[3]);
+      }
+      float acc[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        float lo, hi;
+        unpack_f32x2(acc2[h], lo, hi);
+        acc[h] = lo + hi;
       }
 #pragma unroll
       for (int h = 0; h < 4; ++h) s_bias[h * Tl::kRows + t] = __float2bfloat16_rn(acc[h]);
