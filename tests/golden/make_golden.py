@@ -2,7 +2,7 @@
 
 Run once, in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py <path of the reference checkout>
 
 The function ``dot_product_attention_torch`` is taken verbatim out of the reference's
 ``examples/dot_product_attention.py`` at run time (its source text is parsed, the one function
@@ -75,7 +75,9 @@ def bits(t: torch.Tensor) -> np.ndarray:
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python " + sys.argv[0] + " <path of the reference checkout>")
+    ref_root = sys.argv[1]
     ref_fn = load_reference_function(ref_root)
     out = {}
     for i, (name, B1, B2, S, D, mf, bd, bs) in enumerate(CASES):

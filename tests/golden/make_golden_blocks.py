@@ -1,7 +1,7 @@
 """Generates tests/golden/blocks_golden.npz from the reference's own PyTorch models of the two
 attention blocks.
 
-    python tests/golden/make_golden_blocks.py [/root/reference]
+    python tests/golden/make_golden_blocks.py <path of the reference checkout>
 
 The classes ``AttentionTorch`` of ``examples/grid_self_attention.py`` and
 ``examples/self_attention.py`` are taken out of the reference's files at run time (source parsed,
@@ -33,7 +33,9 @@ def load_class(path: str, name: str):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python " + sys.argv[0] + " <path of the reference checkout>")
+    ref = sys.argv[1]
     out = {}
     Grid = load_class(os.path.join(ref, "examples", "grid_self_attention.py"), "AttentionTorch")
     for tag, N, c_pair, heads, transpose in (("grid_n24_c64_h2", 24, 64, 2, False),
