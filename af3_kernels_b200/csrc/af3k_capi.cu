@@ -553,6 +553,27 @@ int af3k_pair_bias(const void* pair, int32_t pair_dtype, int64_t R, int64_t N, i
   return AF3K_OK;
 }
 
+int af3k_sigmoid_gate(const void* weighted, const void* gate, void* out, int64_t n, void* stream_v) {
+  t_last_launches = 0;
+  if (n < 0 || (n & 7) != 0) return AF3K_ERR_BAD_SHAPE;
+  if (n == 0) return AF3K_OK;
+  if (!weighted || !gate || !out) return AF3K_ERR_NULL_POINTER;
+  if (!aligned16(weighted) || !aligned16(gate) || !aligned16(out)) return AF3K_ERR_BAD_ALIGNMENT;
+  DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev);
+  if (rc != AF3K_OK) return rc;
+  const long long n8 = n / 8;
+  long long blocks = (n8 + 255) / 256;
+  const long long cap = (long long)dev->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  sigmoid_gate_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(
+      static_cast<const uint4*>(weighted), static_cast<const uint4*>(gate), static_cast<uint4*>(out), n8);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail("launch sigmoid_gate_kernel", e);
+  t_last_launches = 1;
+  return AF3K_OK;
+}
+
 int af3k_selftest_wait_timeout(long long limit_cycles, int* status_dev, void* stream_v) {
   if (limit_cycles <= 0) return AF3K_ERR_BAD_SHAPE;
   wait_timeout_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream_v)>>>(limit_cycles,

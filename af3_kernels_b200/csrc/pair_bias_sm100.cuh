@@ -332,4 +332,31 @@ __global__ void __launch_bounds__(PbTile<T>::kRows, 640 / PbTile<T>::kRows) pair
   }
 }
 
+// ---------------------------------------------------------------- sigmoid gate
+// out = weighted * sigmoid(gate), elementwise over bf16 tensors of n elements (n a multiple of 8,
+// pointers 16-byte aligned).  Stands in for the SigmoidFwdTPP + MulTPP pair behind the core in the
+// reference's fused blocks (src/csrc/dot_product_attention.cpp:339-345 and :522-528).  The
+// sigmoid is taken in fp32 and only the product is rounded (the reference rounds the sigmoid to
+// bf16 first).  HBM-bound: 4 bytes read and 2 written per element.
+__global__ void __launch_bounds__(256) sigmoid_gate_kernel(const uint4* __restrict__ weighted,
+                                                           const uint4* __restrict__ gate,
+                                                           uint4* __restrict__ out, long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * blockDim.x) {
+    const uint4 a = weighted[i], g = gate[i];
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+    uint32_t r[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float a0 = __uint_as_float(aw[e] << 16), a1 = __uint_as_float(aw[e] & 0xffff0000u);
+      const float g0 = __uint_as_float(gw[e] << 16), g1 = __uint_as_float(gw[e] & 0xffff0000u);
+      // sigmoid(x) = 1 / (1 + 2^(-x log2 e))
+      const float s0 = __frcp_rn(1.0f + ex2_approx(-1.4426950408889634f * g0));
+      const float s1 = __frcp_rn(1.0f + ex2_approx(-1.4426950408889634f * g1));
+      r[e] = pb_pack_bf16x2(a0 * s0, a1 * s1);
+    }
+    out[i] = make_uint4(r[0], r[1], r[2], r[3]);
+  }
+}
+
 }  // namespace af3k

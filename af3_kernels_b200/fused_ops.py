@@ -22,11 +22,29 @@ from typing import Optional
 
 import torch
 
+from . import _capi
 from .dpa import dot_product_attention
 
 
 def _as_bf16(t: torch.Tensor) -> torch.Tensor:
     return t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)
+
+
+def sigmoid_gate(weighted: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """weighted * sigmoid(gate) for two bf16 CUDA tensors of the same shape, in one pass
+    (``af3k_sigmoid_gate``; reference: the SigmoidFwdTPP + MulTPP pair behind the core,
+    src/csrc/dot_product_attention.cpp:339-345).  Shapes the kernel does not take (element count
+    not a multiple of 8, non-contiguous) go through torch."""
+    n = weighted.numel()
+    if (weighted.dtype != torch.bfloat16 or gate.dtype != torch.bfloat16 or n % 8 != 0 or n == 0
+            or not weighted.is_contiguous() or not gate.is_contiguous()
+            or weighted.data_ptr() % 16 != 0 or gate.data_ptr() % 16 != 0):
+        return weighted * torch.sigmoid(gate)
+    out = torch.empty_like(weighted)
+    with torch.cuda.device(weighted.device):
+        _capi.check(_capi.load().af3k_sigmoid_gate(weighted.data_ptr(), gate.data_ptr(), out.data_ptr(), n,
+                                                   torch.cuda.current_stream().cuda_stream))
+    return out
 
 
 def attention_block(
@@ -56,8 +74,7 @@ def attention_block(
     v = torch.matmul(x, _as_bf16(v_proj)).view(R, N, head, D).permute(0, 2, 1, 3)
     weighted = torch.empty((R, N, head, D), dtype=torch.bfloat16, device=pair.device)
     dot_product_attention(q, k, v, mask, bias, out=weighted.permute(0, 2, 1, 3))
-    gate = torch.sigmoid(torch.matmul(x, _as_bf16(gating_query)))
-    gated = weighted.view(R, N, C) * gate
+    gated = sigmoid_gate(weighted.view(R, N, C), torch.matmul(x, _as_bf16(gating_query)))
     return torch.matmul(gated, _as_bf16(out_proj)).to(pair.dtype)
 
 
@@ -89,5 +106,4 @@ def self_attention_block(
     weighted = torch.empty((1, N, head, D), dtype=torch.bfloat16, device=x.device)
     m = None if mask is None else mask.reshape(-1)
     dot_product_attention(q, k, v, m, bias, out=weighted.permute(0, 2, 1, 3))
-    gate = torch.sigmoid(torch.matmul(xb, _as_bf16(gating_query)))
-    return (weighted.view(N, C) * gate).to(x.dtype)
+    return sigmoid_gate(weighted.view(N, C), torch.matmul(xb, _as_bf16(gating_query))).to(x.dtype)

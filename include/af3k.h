@@ -168,6 +168,12 @@ int af3k_pair_bias(const void* pair, int32_t pair_dtype, int64_t R, int64_t N, i
                    const float* gamma, const float* beta, const float* proj, float eps, void* normed,
                    void* bias, int64_t bias_pitch, void* stream);
 
+/* out = weighted * sigmoid(gate), elementwise over n bf16 elements (n a multiple of 8; all three
+ * pointers 16-byte aligned; out may be weighted).  Stands in for the SigmoidFwdTPP + MulTPP pair
+ * behind the attention core in the reference's fused blocks
+ * (src/csrc/dot_product_attention.cpp:339-345 and :522-528). */
+int af3k_sigmoid_gate(const void* weighted, const void* gate, void* out, int64_t n, void* stream);
+
 /* Self-test of the bounded wait: launches one block that waits, with the given limit, on a
  * barrier nothing ever arrives at, and writes AF3K_STATUS_WAIT_TIMEOUT to status_dev when the
  * wait gives up.  No counterpart in the reference (it has no device code). */

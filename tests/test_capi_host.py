@@ -170,3 +170,12 @@ def test_pair_bias_argument_validation_codes():
     assert lib.af3k_pair_bias(*args(pitch=7)) == 3          # pitch < N
     assert lib.af3k_pair_bias(*args(N=8, pitch=12)) == 3    # pitch not a multiple of 8
     assert lib.af3k_pair_bias(*args(R=0)) == 0              # empty problem
+
+
+def test_sigmoid_gate_argument_validation_codes():
+    lib = _capi.load()
+    one = ctypes.c_void_p(16)
+    assert lib.af3k_sigmoid_gate(one, one, one, 12, None) == 2          # not a multiple of 8
+    assert lib.af3k_sigmoid_gate(one, one, one, 0, None) == 0           # empty
+    assert lib.af3k_sigmoid_gate(None, one, one, 8, None) == 6
+    assert lib.af3k_sigmoid_gate(ctypes.c_void_p(8), one, one, 8, None) == 4

@@ -81,3 +81,19 @@ def test_pair_bias_feeds_attention_in_place(cuda_device):
     ref = O.oracle_fp32(q.cpu(), q.cpu(), q.cpu(), None, bias.cpu())
     st = O.error_stats(out.cpu(), ref)
     assert st["nan"] == 0 and st["max_abs"] <= 2e-2, st
+
+
+def test_sigmoid_gate_matches_fp32(cuda_device):
+    from af3_kernels_b200.fused_ops import sigmoid_gate
+    g = torch.Generator().manual_seed(3)
+    for shape in ((5, 37, 128), (1, 8), (300, 264)):
+        w = (torch.randn(*shape, generator=g) * 2).to(torch.bfloat16).to(cuda_device)
+        x = (torch.randn(*shape, generator=g) * 6).to(torch.bfloat16).to(cuda_device)
+        x.view(-1)[:4] = torch.tensor([-200.0, 200.0, 0.0, -30.0], dtype=torch.bfloat16)
+        out = sigmoid_gate(w, x)
+        ref = w.float() * torch.sigmoid(x.float())
+        assert out.dtype == torch.bfloat16 and torch.isfinite(out.float()).all()
+        assert ((out.float() - ref).abs() <= 2.0 ** -7 * ref.abs() + 1e-6).all()      # one bf16 ulp
+    # shapes the kernel does not take go through torch and agree as well
+    w = torch.randn(3, 5, device=cuda_device).to(torch.bfloat16)
+    assert torch.equal(sigmoid_gate(w, w), w * torch.sigmoid(w))
