@@ -13,6 +13,7 @@ import torch
 
 from . import _capi
 from .dpa import dot_product_attention, dot_product_attention_host, read_status
+from . import tools
 from .tools import pad_to_size, print_comm_time, profile, record_comm_time
 from .distributed import RowShardedAttention, row_partition
 from .fused_ops import attention_block, self_attention_block
@@ -36,6 +37,10 @@ __all__ = [
     "reset_debug_timers",
     "print_debug_timers",
     "print_debug_thread_imbalance",
+    "Linear",
+    "TriangleMultiplicationCpp",
+    "DistributedTriangleMultiplicationCpp",
+    "read_status",
 ]
 
 
@@ -146,12 +151,62 @@ def vnni_repack_tensor(x: torch.Tensor, type: int = 2, BLK_SZ: int = 0) -> torch
 
 
 def reset_debug_timers():
-    """The reference resets per-thread rdtsc timers (src/csrc/init.cpp:102-143); kept as a no-op."""
+    """The reference resets its per-thread rdtsc timers (src/csrc/init.cpp:102-143); here the
+    per-operator CUDA-event totals gathered by the ``profile`` wrapper are cleared."""
+    tools.reset_op_timers()
 
 
 def print_debug_timers(tid=0, detailed=True):
-    """No CPU-thread timers exist here; use CUDA events or torch.profiler (DO_PROFILE=1)."""
+    """Prints per-operator call counts and device milliseconds (CUDA events around every wrapped
+    operator; gathered when DO_PROFILE=1 or AF3K_TIMERS=1).  The reference prints per-TPP-category
+    CPU-thread timers (src/csrc/init.cpp:145-216); ``tid`` selects a CPU thread there and is
+    ignored here."""
+    totals = tools.op_timer_totals()
+    if not totals:
+        print("af3k timers: nothing recorded (set DO_PROFILE=1 or AF3K_TIMERS=1 before importing)")
+        return
+    print(f"{'operator':<32}{'calls':>8}{'total ms':>12}{'ms/call':>12}")
+    for name, (calls, ms) in sorted(totals.items()):
+        print(f"{name:<32}{calls:>8}{ms:>12.3f}{(ms / calls if calls else 0.0):>12.4f}")
 
 
 def print_debug_thread_imbalance():
-    """See print_debug_timers."""
+    """The reference prints the spread of its OpenMP threads' timers (src/csrc/init.cpp:218-309).
+    A kernel launch has no host threads to compare; the per-operator table is printed instead."""
+    print_debug_timers()
+
+
+class Linear(torch.nn.Module):
+    """Bias-free linear layer with the reference's constructor (src/af3_kernels/__init__.py:138-165).
+    Outside the attention hot path: a plain cuBLAS GEMM on the tensor's device, no VNNI repack."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=None,
+                 M_BLK: int = 128, N_BLK: int = 128) -> None:
+        super().__init__()
+        assert bias is False
+        self.in_features = in_features
+        self.out_features = out_features
+        self.weight = torch.nn.Parameter(torch.empty((out_features, in_features), device=device, dtype=dtype))
+        self.register_parameter("bias", None)
+        self.M_BLK = M_BLK
+        self.N_BLK = N_BLK
+
+    def forward(self, input: torch.Tensor) -> torch.Tensor:
+        return torch.nn.functional.linear(input, self.weight)
+
+
+class TriangleMultiplicationCpp(torch.nn.Module):
+    """Importable for code that names it (src/af3_kernels/TriangleMultiplication.py:22-76); the
+    triangle multiplication is a different operator from the attention path built here."""
+
+    def __init__(self, *args, **kwargs) -> None:
+        super().__init__()
+        _not_built("TriangleMultiplicationCpp")
+
+
+class DistributedTriangleMultiplicationCpp(torch.nn.Module):
+    """See TriangleMultiplicationCpp (src/af3_kernels/TriangleMultiplication.py:79-192)."""
+
+    def __init__(self, *args, **kwargs) -> None:
+        super().__init__()
+        _not_built("DistributedTriangleMultiplicationCpp")

@@ -141,6 +141,14 @@ int validate(const af3k_attention_desc& d) {
     return AF3K_ERR_BAD_STRIDE;
   if (d.bias_stride[0] < 0 || d.bias_stride[1] < d.Sk || d.mask_row_stride < 0)
     return AF3K_ERR_BAD_STRIDE;
+  // A zero stride (a broadcast view) is only meaningful on a dimension of extent 1: TMA cannot
+  // express it, and a zero output stride would make rows overwrite each other.
+  const int64_t ext_q[3] = {d.B1, d.B2, d.Sq}, ext_k[3] = {d.B1, d.B2, d.Sk};
+  for (int i = 0; i < 3; ++i) {
+    if (ext_q[i] > 1 && (d.q_stride[i] == 0 || d.out_stride[i] == 0)) return AF3K_ERR_BAD_STRIDE;
+    if (ext_k[i] > 1 && (d.k_stride[i] == 0 || d.v_stride[i] == 0)) return AF3K_ERR_BAD_STRIDE;
+  }
+  if (d.B2 > 1 && d.bias_stride[0] == 0) return AF3K_ERR_BAD_STRIDE;
   return AF3K_OK;
 }
 

@@ -825,7 +825,10 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
     // ---- epilogue: O / l -> bf16 -> global, once this warpgroup's last P V has finished (the
     // other warpgroup may still be working on its own streams)
     if (kDebug && last_ts != nullptr) last_ts[5] = clock64();
-    if (ucnt > 0) AF3K_WAIT_WARP(c, BarIdx::kv_empty + (int)prev_stage, prev_round & 1);
+    // only a warpgroup that had a stream in this item has a P V of this item to wait for (with an
+    // odd row count the last item leaves warpgroup 1 without one: its record of a previous tile
+    // may be a whole number of ring laps old, and the parity test would then wait for ever)
+    if (wg < it.gv) AF3K_WAIT_WARP(c, BarIdx::kv_empty + (int)prev_stage, prev_round & 1);
     tc_fence_after();
     if (kDebug && last_ts != nullptr) last_ts[6] = clock64();
     const int qrow = it.qt * kTile + row;

@@ -105,8 +105,17 @@ def dot_product_attention(
         if q_scale.numel() != B2 or k_scale.numel() != B2:
             raise ValueError("q_scale / k_scale must have one entry per head")
     else:
+        if q.dtype == torch.float32:
+            # the reference has an fp32 instantiation (src/csrc/dot_product_attention.cpp:554-558);
+            # here fp32 callers get the bf16 kernel (operands rounded once) and an fp32 result
+            if out is not None:
+                raise ValueError("`out` must be omitted with fp32 q (the result is converted from the kernel's bf16 output)")
+            return dot_product_attention(
+                q.to(torch.bfloat16), k, v, mask, bias, softmax_scale=softmax_scale,
+                rows_per_item=rows_per_item, check_status=check_status, use_workspace=use_workspace,
+            ).to(torch.float32)
         if q.dtype != torch.bfloat16:
-            raise TypeError(f"q must be bfloat16 or float8_e4m3fn, got {q.dtype}")
+            raise TypeError(f"q must be bfloat16, float32 or float8_e4m3fn, got {q.dtype}")
         if q_scale is not None or k_scale is not None:
             raise TypeError("q_scale / k_scale are only valid with fp8 q and k")
         if k.dtype != torch.bfloat16:
@@ -118,11 +127,16 @@ def dot_product_attention(
     if bias.dtype not in (torch.bfloat16, torch.float32):
         bias = bias.to(torch.float32)
     bias = bias.reshape(B2, Sq, Sk) if bias.dim() != 3 else bias
-    if Sk > 1 and bias.stride(2) != 1:
+    if (Sk > 1 and bias.stride(2) != 1) or (B2 > 1 and bias.stride(0) == 0) or (Sq > 1 and bias.stride(1) == 0):
         bias = bias.contiguous()
 
     def _inner_contig(t):
-        return t if (t.stride(3) == 1 or t.shape[3] == 1) else t.contiguous()
+        # unit innermost stride; a broadcast (zero-stride) view cannot be described to TMA
+        if t.shape[3] != 1 and t.stride(3) != 1:
+            return t.contiguous()
+        if any(t.stride(i) == 0 and t.shape[i] > 1 for i in range(3)):
+            return t.contiguous()
+        return t
 
     q, k, v = _inner_contig(q), _inner_contig(k), _inner_contig(v)
     mask_u8, mask_stride = _mask_rows(mask, B1, Sk)

@@ -10,17 +10,67 @@ DO_PROFILE = environ.get("DO_PROFILE", "0") == "1"
 USE_DIST = environ.get("USE_DIST", "0") == "1"
 
 
+# Per-operator device time, gathered when DO_PROFILE=1 or AF3K_TIMERS=1: name -> [calls, [(start, end) CUDA
+# events not yet folded in], milliseconds folded in].  The reference keeps per-thread rdtsc
+# timers per TPP category (src/csrc/timing.h:232-265) and prints them with print_debug_timers
+# (src/csrc/init.cpp:145-216); on the GPU the unit that can be timed from the host is the operator.
+DO_TIMERS = DO_PROFILE or environ.get("AF3K_TIMERS", "0") == "1"
+op_timers: dict = {}
+
+
+def _fold(entry) -> None:
+    pending = entry[1]
+    if pending:
+        pending[-1][1].synchronize()
+        entry[2] += sum(a.elapsed_time(b) for a, b in pending)
+        pending.clear()
+
+
+def reset_op_timers() -> None:
+    op_timers.clear()
+
+
+def op_timer_totals() -> dict:
+    """name -> (calls, total milliseconds on the device); waits for the recorded events."""
+    out = {}
+    for name, entry in op_timers.items():
+        _fold(entry)
+        out[name] = (entry[0], entry[2])
+    return out
+
+
 def profile(name: str = None):
-    """Wraps a function in a torch.profiler range when DO_PROFILE=1 (reference: tools.py:20-33)."""
+    """With DO_PROFILE=1: wraps a function in a torch.profiler range (reference: tools.py:20-33)
+    and an NVTX range, and brackets it with CUDA events on the current stream so that
+    ``print_debug_timers`` can print per-operator device time.  With AF3K_TIMERS=1 only the
+    events are recorded.  Otherwise the function is returned unchanged (no overhead)."""
 
     def decorator(func):
-        if not DO_PROFILE:
+        if not DO_TIMERS:
             return func
+        label = func.__name__ if name is None else name
 
         @wraps(func)
         def wrapper(*args, **kwargs):
-            with torch.profiler.record_function(func.__name__ if name is None else name):
+            cuda = torch.cuda.is_available()
+            if cuda:
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                torch.cuda.nvtx.range_push(label)
+            try:
+                if DO_PROFILE:
+                    with torch.profiler.record_function(label):
+                        return func(*args, **kwargs)
                 return func(*args, **kwargs)
+            finally:
+                if cuda:
+                    torch.cuda.nvtx.range_pop()
+                    end.record()
+                    entry = op_timers.setdefault(label, [0, [], 0.0])
+                    entry[0] += 1
+                    entry[1].append((start, end))
+                    if len(entry[1]) >= 256:
+                        _fold(entry)
 
         return wrapper
 

@@ -83,6 +83,42 @@ def test_argument_validation_codes():
     assert lib.af3k_dot_product_attention(None, *([None] * 9), 0, None, None) == 6
 
 
+def test_zero_strides_are_rejected_unless_the_extent_is_one():
+    # a broadcast view (stride 0) cannot be described to TMA, and a zero output stride would make
+    # rows overwrite each other: refused unless the dimension has one entry
+    lib = _capi.load()
+    out = (ctypes.c_int32 * 6)()
+    for field in ("q_stride", "k_stride", "v_stride", "out_stride"):
+        for dim in (0, 1):
+            d = _desc(4, 2, 128, 32)
+            getattr(d, field)[dim] = 0
+            assert lib.af3k_describe_plan(ctypes.byref(d), out) == 3, (field, dim)
+    d = _desc(4, 2, 128, 32)
+    d.bias_stride[0] = 0
+    assert lib.af3k_describe_plan(ctypes.byref(d), out) == 3
+    ok = _desc(1, 1, 128, 32)                      # extent-1 dimensions may carry any stride
+    for field in ("q_stride", "k_stride", "v_stride", "out_stride"):
+        getattr(ok, field)[0] = 0
+        getattr(ok, field)[1] = 0
+    ok.bias_stride[0] = 0
+    assert lib.af3k_describe_plan(ctypes.byref(ok), out) == 0
+
+
+def test_boundary_names_of_the_reference_import():
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "src"))
+    import af3_kernels as K
+    for name in ("Linear", "TriangleMultiplicationCpp", "DistributedTriangleMultiplicationCpp",
+                 "GridSelfAttentionCpp", "DistributedGridSelfAttentionCpp"):
+        assert hasattr(K, name), name
+    lin = K.Linear(8, 4, bias=False)
+    assert lin.weight.shape == (4, 8)
+    with pytest.raises(NotImplementedError):
+        K.TriangleMultiplicationCpp(128)
+    with pytest.raises(NotImplementedError):
+        K.DistributedTriangleMultiplicationCpp(128)
+
+
 def test_workspace_size_rules():
     lib = _capi.load()
     f32 = _desc(1, 16, 512, 32, bias_dtype=_capi.AF3K_F32)
