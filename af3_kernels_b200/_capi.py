@@ -23,6 +23,7 @@ EXPORTED_SYMBOLS = (
     "af3k_strerror",
     "af3k_last_error_detail",
     "af3k_dot_product_attention_workspace",
+    "af3k_stage_bias",
     "af3k_dot_product_attention",
     "af3k_dot_product_attention_noalloc",
     "af3k_static_scratch_bytes",
@@ -55,6 +56,8 @@ class AttentionDesc(ctypes.Structure):
         ("bias_dtype", ctypes.c_int32),
         ("softmax_scale", ctypes.c_float),
         ("rows_per_item", ctypes.c_int32),
+        ("bias_prescaled", ctypes.c_int32),
+        ("reserved_", ctypes.c_int32),
     ]
 
 
@@ -88,6 +91,8 @@ def load() -> ctypes.CDLL:
     lib.af3k_last_error_detail.argtypes = []
     lib.af3k_dot_product_attention_workspace.restype = sz
     lib.af3k_dot_product_attention_workspace.argtypes = [dp, vp]
+    lib.af3k_stage_bias.restype = ctypes.c_int
+    lib.af3k_stage_bias.argtypes = [dp, vp, vp, vp, vp, sz, vp]
     lib.af3k_dot_product_attention.restype = ctypes.c_int
     lib.af3k_dot_product_attention.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp, vp]
     lib.af3k_dot_product_attention_noalloc.restype = ctypes.c_int

@@ -129,6 +129,9 @@ int validate(const af3k_attention_desc& d) {
   if (d.B1 > 0x7fffffff || d.B2 > 0x7fffffff || d.Sq > 0x7fffff00 || d.Sk > 0x7fffff00)
     return AF3K_ERR_BAD_SHAPE;
   if (d.rows_per_item < 0 || d.rows_per_item > 8) return AF3K_ERR_BAD_SHAPE;   // a request, clamped by the plan
+  if (d.bias_prescaled != 0 && (d.bias_prescaled != 1 || d.qk_dtype != AF3K_FP8_E4M3 || d.bias_dtype != AF3K_BF16))
+    return AF3K_ERR_BAD_DTYPE;
+  if (d.reserved_ != 0) return AF3K_ERR_BAD_SHAPE;
   const int64_t es = d.qk_dtype == AF3K_FP8_E4M3 ? 1 : 2;
   for (int i = 0; i < 3; ++i) {
     if (d.q_stride[i] < 0 || d.k_stride[i] < 0 || d.v_stride[i] < 0 || d.out_stride[i] < 0)
@@ -326,7 +329,7 @@ int static_scratch_address(void** out) {
 
 extern "C" {
 
-int af3k_version(void) { return 1000; }
+int af3k_version(void) { return 1001; }
 
 const char* af3k_strerror(int code) {
   switch (code) {
@@ -347,7 +350,7 @@ const char* af3k_strerror(int code) {
 size_t af3k_dot_product_attention_workspace(const af3k_attention_desc* desc, const void* bias) {
   if (desc == nullptr || validate(*desc) != AF3K_OK) return 0;
   // fp8 q/k: the staging copy is what lets the tensor core add the bias (optional, see the entry)
-  if (!bias_needs_staging(*desc, bias) && desc->qk_dtype != AF3K_FP8_E4M3) return 0;
+  if (!bias_needs_staging(*desc, bias) && (desc->qk_dtype != AF3K_FP8_E4M3 || desc->bias_prescaled)) return 0;
   return (size_t)desc->B2 * desc->Sq * staged_bias_pitch(desc->Sk) * 2;
 }
 
@@ -356,6 +359,47 @@ int af3k_last_launch_count(void) { return t_last_launches; }
 const char* af3k_last_error_detail(void) { return t_detail; }
 
 void af3k_set_wait_limit_cycles(long long cycles) { g_wait_limit.store(cycles > 0 ? cycles : -1); }
+
+namespace {
+int launch_bias_staging(const af3k_attention_desc& d, const DeviceInfo& dev, const void* bias, const float* sq,
+                        const float* sk, void* staged, cudaStream_t stream) {
+  const int64_t pitch = staged_bias_pitch(d.Sk);
+  const long long total = (long long)d.B2 * d.Sq * (pitch / 2);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > dev.sm_count * 16) blocks = dev.sm_count * 16;
+  if (d.bias_dtype == AF3K_F32)
+    bias_to_bf16_kernel<float><<<blocks, 256, 0, stream>>>(
+        static_cast<const float*>(bias), static_cast<__nv_bfloat16*>(staged), (int)d.B2, (int)d.Sq,
+        (int)d.Sk, d.bias_stride[0], d.bias_stride[1], (int)pitch, sq, sk, d.softmax_scale);
+  else
+    bias_to_bf16_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(staged), (int)d.B2,
+        (int)d.Sq, (int)d.Sk, d.bias_stride[0], d.bias_stride[1], (int)pitch, sq, sk, d.softmax_scale);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? AF3K_OK : cuda_fail("launch bias_to_bf16_kernel", e);
+}
+}  // namespace
+
+int af3k_stage_bias(const af3k_attention_desc* desc, const void* bias, const float* q_scale,
+                    const float* k_scale, void* staged, size_t staged_bytes, void* stream_v) {
+  t_last_launches = 0;
+  if (desc == nullptr) return AF3K_ERR_NULL_POINTER;
+  af3k_attention_desc d = *desc;
+  d.bias_prescaled = 0;      // describes the input bias here
+  int rc = validate(d);
+  if (rc != AF3K_OK) return rc;
+  if (d.B2 == 0 || d.Sq == 0) return AF3K_OK;
+  if (!bias || !staged) return AF3K_ERR_NULL_POINTER;
+  if ((q_scale != nullptr) != (k_scale != nullptr)) return AF3K_ERR_BAD_DTYPE;
+  if (q_scale != nullptr && d.qk_dtype != AF3K_FP8_E4M3) return AF3K_ERR_BAD_DTYPE;
+  if (!aligned16(staged)) return AF3K_ERR_BAD_ALIGNMENT;
+  if (staged_bytes < (size_t)d.B2 * d.Sq * staged_bias_pitch(d.Sk) * 2) return AF3K_ERR_WORKSPACE;
+  DeviceInfo* dev = nullptr;
+  if ((rc = device_info(&dev)) != AF3K_OK) return rc;
+  rc = launch_bias_staging(d, *dev, bias, q_scale, k_scale, staged, reinterpret_cast<cudaStream_t>(stream_v));
+  if (rc == AF3K_OK) t_last_launches = 1;
+  return rc;
+}
 
 int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, const void* k,
                                const void* v, const void* bias, const uint8_t* mask, void* out,
@@ -392,28 +436,17 @@ int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, c
   // bias in fp32 as before
   const size_t stage_bytes = (size_t)d.B2 * d.Sq * staged_bias_pitch(d.Sk) * 2;
   const bool must_stage = bias_needs_staging(d, bias);
-  const bool fp8_tc = fp8 && workspace != nullptr && workspace_bytes >= stage_bytes && aligned16(workspace);
-  if (must_stage || fp8_tc) {
-    const int64_t pitch = staged_bias_pitch(d.Sk);
-    const size_t need = stage_bytes;
-    if (workspace == nullptr || workspace_bytes < need) return AF3K_ERR_WORKSPACE;
+  if (d.bias_prescaled && must_stage) return AF3K_ERR_BAD_STRIDE;   // a staged copy is TMA-addressable by construction
+  const bool stage_fp8 = fp8 && !d.bias_prescaled && workspace != nullptr && workspace_bytes >= stage_bytes &&
+                         aligned16(workspace);
+  const bool fp8_tc = fp8 && (d.bias_prescaled || stage_fp8);
+  if (must_stage || stage_fp8) {
+    if (workspace == nullptr || workspace_bytes < stage_bytes) return AF3K_ERR_WORKSPACE;
     if (!aligned16(workspace)) return AF3K_ERR_BAD_ALIGNMENT;
-    const float* sq = fp8_tc ? q_scale : nullptr;
-    const float* sk = fp8_tc ? k_scale : nullptr;
-    const long long total = (long long)d.B2 * d.Sq * (pitch / 2);
-    int blocks = (int)((total + 255) / 256);
-    if (blocks > dev->sm_count * 16) blocks = dev->sm_count * 16;
-    if (d.bias_dtype == AF3K_F32)
-      bias_to_bf16_kernel<float><<<blocks, 256, 0, stream>>>(
-          static_cast<const float*>(bias), static_cast<__nv_bfloat16*>(workspace), (int)d.B2,
-          (int)d.Sq, (int)d.Sk, d.bias_stride[0], d.bias_stride[1], (int)pitch, sq, sk, d.softmax_scale);
-    else
-      bias_to_bf16_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
-          static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(workspace),
-          (int)d.B2, (int)d.Sq, (int)d.Sk, d.bias_stride[0], d.bias_stride[1], (int)pitch, sq, sk,
-          d.softmax_scale);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail("launch bias_to_bf16_kernel", e);
+    const int64_t pitch = staged_bias_pitch(d.Sk);
+    if ((rc = launch_bias_staging(d, *dev, bias, stage_fp8 ? q_scale : nullptr, stage_fp8 ? k_scale : nullptr,
+                                  workspace, stream)) != AF3K_OK)
+      return rc;
     ++launches;
     bias_base = workspace;
     bias_sr = pitch;
@@ -507,6 +540,10 @@ int af3k_dot_product_attention_noalloc(const af3k_attention_desc* desc, const vo
                   kStaticScratchBytes);
     return AF3K_ERR_SCRATCH_LIMIT;
   }
+  // the device check comes first, so that a GPU this library has no code for is reported as
+  // such and not as a failed symbol lookup
+  DeviceInfo* dev = nullptr;
+  if ((rc = device_info(&dev)) != AF3K_OK) return rc;
   void* scratch = nullptr;
   if (need != 0 && (rc = static_scratch_address(&scratch)) != AF3K_OK) return rc;
   // From here on this is the ordinary call with the built-in array as its workspace.  The

@@ -7,9 +7,11 @@ with raw device pointers on the current CUDA stream.  There is no CPU path.
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 import math
 import os
+import weakref
 from typing import Optional
 
 import torch
@@ -35,6 +37,93 @@ def read_status(device: torch.device) -> list:
     vals = buf.cpu().tolist()
     buf.zero_()
     return vals
+
+
+class StagedBias:
+    """A bias converted once into the form the kernel reads in place (bf16, rows padded to 16
+    bytes; with fp8 q/k also divided by each head's logit scale).  Made by ``stage_bias``; pass it
+    to ``dot_product_attention`` instead of the bias tensor."""
+
+    def __init__(self, data: torch.Tensor, B2: int, Sq: int, Sk: int, prescaled: bool):
+        self.data, self.B2, self.Sq, self.Sk, self.prescaled = data, B2, Sq, Sk, prescaled
+
+
+def stage_bias(bias: torch.Tensor, B2: int, Sq: int, Sk: int, *, q_scale=None, k_scale=None,
+               softmax_scale: Optional[float] = None, head_dim: int = 32) -> StagedBias:
+    """Runs the bias staging pass on its own (``af3k_stage_bias``) on the current stream, for a
+    bias that is applied in many calls: those calls then launch one kernel instead of two.
+    ``softmax_scale`` / ``head_dim`` matter only with fp8 scales (the copy is divided by
+    ``softmax_scale * q_scale[h] * k_scale[h]``, default scale ``1/sqrt(head_dim)``)."""
+    if not bias.is_cuda:
+        raise RuntimeError("af3_kernels_b200 runs on CUDA tensors only (no CPU fallback)")
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    prescaled = False
+    if not isinstance(bias, StagedBias):
+        if bias.numel() != B2 * Sq * Sk:
+            raise ValueError(f"bias must have B2*Sq*Sk = {B2 * Sq * Sk} elements, got {bias.numel()}")
+        needs_copy = (bias.dtype != torch.bfloat16 or bias.dim() != 3 or bias.stride(-1) != 1
+                      or (bias.stride(-2) * 2) % 16 != 0 or (bias.stride(0) * 2) % 16 != 0
+                      or bias.data_ptr() % 16 != 0)
+        if use_workspace and cache_bias and (needs_copy or fp8):
+            bias = _cached_stage(bias, B2, Sq, Sk, D, q_scale if fp8 else None, k_scale if fp8 else None, scale)
+    if isinstance(bias, StagedBias):
+        if (bias.B2, bias.Sq, bias.Sk) != (B2, Sq, Sk) or bias.prescaled != fp8:
+            raise ValueError("staged bias was made for another shape or another q/k type")
+        prescaled = bias.prescaled
+        bias = bias.data[:, :, :Sk]
+    else:
+        if bias.dtype not in (torch.bfloat16, torch.float32):
+            bias = bias.to(torch.float32)
+        bias = bias.reshape(B2, Sq, Sk) if bias.dim() != 3 else bias
+        if (Sk > 1 and bias.stride(2) != 1) or (B2 > 1 and bias.stride(0) == 0) or (Sq > 1 and bias.stride(1) == 0):
+            bias = bias.contiguous()
+    fp8 = q_scale is not None
+    desc = _capi.AttentionDesc()
+    desc.B1, desc.B2, desc.Sq, desc.Sk, desc.D = 1, B2, Sq, Sk, 16 * ((head_dim + 15) // 16)
+    for name in ("q_stride", "k_stride", "v_stride", "out_stride"):
+        getattr(desc, name)[:] = [B2 * max(Sq, Sk) * 64, max(Sq, Sk) * 64, 64]
+    desc.bias_stride[:] = [bias.stride(0), bias.stride(1)]
+    desc.qk_dtype = _capi.AF3K_FP8_E4M3 if fp8 else _capi.AF3K_BF16
+    desc.bias_dtype = _capi.AF3K_BF16 if bias.dtype == torch.bfloat16 else _capi.AF3K_F32
+    desc.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(head_dim)
+    pitch = (Sk + 7) // 8 * 8
+    staged = torch.empty((B2, Sq, pitch), dtype=torch.bfloat16, device=bias.device)
+    if fp8:
+        q_scale = q_scale.to(device=bias.device, dtype=torch.float32).contiguous()
+        k_scale = k_scale.to(device=bias.device, dtype=torch.float32).contiguous()
+    with torch.cuda.device(bias.device):
+        _capi.check(_capi.load().af3k_stage_bias(
+            ctypes.byref(desc), bias.data_ptr(), q_scale.data_ptr() if fp8 else None,
+            k_scale.data_ptr() if fp8 else None, staged.data_ptr(), staged.numel() * 2,
+            torch.cuda.current_stream().cuda_stream))
+    return StagedBias(staged, B2, Sq, Sk, fp8)
+
+
+# Staged copies of recently used biases, so that a caller that applies one bias tensor in many
+# calls (every pair row block of a grid attention, every step of the diffusion transformer) pays
+# for the conversion once.  An entry is valid while the very same tensor object is alive and
+# unmodified (its version counter) and, for fp8, the same scale tensors and softmax scale are used.
+_STAGED_CACHE_SIZE = 4
+_staged_cache: "collections.OrderedDict" = collections.OrderedDict()
+
+
+def _version(t) -> int:
+    return -1 if t is None else t._version
+
+
+def _cached_stage(bias, B2, Sq, Sk, D, q_scale, k_scale, scale) -> StagedBias:
+    key = id(bias)
+    sig = (_version(bias), tuple(bias.shape), tuple(bias.stride()), bias.dtype, bias.data_ptr(), B2, Sq, Sk,
+           None if q_scale is None else (id(q_scale), q_scale._version, id(k_scale), k_scale._version, scale))
+    hit = _staged_cache.get(key)
+    if hit is not None and hit[0]() is bias and hit[1] == sig:
+        _staged_cache.move_to_end(key)
+        return hit[2]
+    staged = stage_bias(bias, B2, Sq, Sk, q_scale=q_scale, k_scale=k_scale, softmax_scale=scale, head_dim=D)
+    _staged_cache[key] = (weakref.ref(bias), sig, staged, q_scale, k_scale)
+    while len(_staged_cache) > _STAGED_CACHE_SIZE:
+        _staged_cache.popitem(last=False)
+    return staged
 
 
 def _mask_rows(mask: Optional[torch.Tensor], B1: int, Sk: int):
@@ -76,6 +165,7 @@ def dot_product_attention(
     out: Optional[torch.Tensor] = None,
     check_status: Optional[bool] = None,
     use_workspace: bool = True,
+    cache_bias: bool = True,
 ) -> torch.Tensor:
     """softmax(scale * q k^T + bias, key-masked) v on the current CUDA stream.
 
@@ -84,13 +174,16 @@ def dot_product_attention(
     every b1.  mask: see ``_mask_rows``.  Returns a new bf16 tensor; inputs are not modified.
     ``use_workspace=False`` hands the library no scratch: a bias that needs a staging copy (fp32, or
     rows that are not 16-byte aligned) is then refused, and fp8 q/k run on the kernel variant whose
-    softmax threads add the bias themselves.
+    softmax threads add the bias themselves.  ``bias`` may be a ``StagedBias``; a plain tensor
+    that needs the staging pass is staged once and the copy is reused while the same, unmodified
+    tensor object keeps being passed (``cache_bias=False`` stages inside every call instead).
     """
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
         raise ValueError("q, k, v must be 4-D [B1, B2, S, D]")
     if not q.is_cuda:
         raise RuntimeError("af3_kernels_b200 runs on CUDA tensors only (no CPU fallback)")
-    if k.device != q.device or v.device != q.device or bias.device != q.device:
+    bias_dev = bias.data.device if isinstance(bias, StagedBias) else bias.device
+    if k.device != q.device or v.device != q.device or bias_dev != q.device:
         raise ValueError("q, k, v, bias must live on the same device")
     B1, B2, Sq, D = q.shape
     Sk = k.shape[2]
@@ -122,13 +215,27 @@ def dot_product_attention(
             k = k.to(torch.bfloat16)
     if v.dtype != torch.bfloat16:
         v = v.to(torch.bfloat16)
-    if bias.numel() != B2 * Sq * Sk:
-        raise ValueError(f"bias must have B2*Sq*Sk = {B2 * Sq * Sk} elements, got {bias.numel()}")
-    if bias.dtype not in (torch.bfloat16, torch.float32):
-        bias = bias.to(torch.float32)
-    bias = bias.reshape(B2, Sq, Sk) if bias.dim() != 3 else bias
-    if (Sk > 1 and bias.stride(2) != 1) or (B2 > 1 and bias.stride(0) == 0) or (Sq > 1 and bias.stride(1) == 0):
-        bias = bias.contiguous()
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    prescaled = False
+    if not isinstance(bias, StagedBias):
+        if bias.numel() != B2 * Sq * Sk:
+            raise ValueError(f"bias must have B2*Sq*Sk = {B2 * Sq * Sk} elements, got {bias.numel()}")
+        needs_copy = (bias.dtype != torch.bfloat16 or bias.dim() != 3 or bias.stride(-1) != 1
+                      or (bias.stride(-2) * 2) % 16 != 0 or (bias.stride(0) * 2) % 16 != 0
+                      or bias.data_ptr() % 16 != 0)
+        if use_workspace and cache_bias and (needs_copy or fp8):
+            bias = _cached_stage(bias, B2, Sq, Sk, D, q_scale if fp8 else None, k_scale if fp8 else None, scale)
+    if isinstance(bias, StagedBias):
+        if (bias.B2, bias.Sq, bias.Sk) != (B2, Sq, Sk) or bias.prescaled != fp8:
+            raise ValueError("staged bias was made for another shape or another q/k type")
+        prescaled = bias.prescaled
+        bias = bias.data[:, :, :Sk]
+    else:
+        if bias.dtype not in (torch.bfloat16, torch.float32):
+            bias = bias.to(torch.float32)
+        bias = bias.reshape(B2, Sq, Sk) if bias.dim() != 3 else bias
+        if (Sk > 1 and bias.stride(2) != 1) or (B2 > 1 and bias.stride(0) == 0) or (Sq > 1 and bias.stride(1) == 0):
+            bias = bias.contiguous()
 
     def _inner_contig(t):
         # unit innermost stride; a broadcast (zero-stride) view cannot be described to TMA
@@ -158,8 +265,9 @@ def dot_product_attention(
     desc.mask_row_stride = mask_stride
     desc.qk_dtype = _capi.AF3K_FP8_E4M3 if fp8 else _capi.AF3K_BF16
     desc.bias_dtype = _capi.AF3K_BF16 if bias.dtype == torch.bfloat16 else _capi.AF3K_F32
-    desc.softmax_scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    desc.softmax_scale = scale
     desc.rows_per_item = int(rows_per_item)
+    desc.bias_prescaled = 1 if prescaled else 0
 
     lib = _capi.load()
     with torch.cuda.device(q.device):

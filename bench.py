@@ -3,16 +3,21 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
 
-One "step" is one attention call over one batch of seeded synthetic input.  At N = 1 the
-workload is grid / triangle self-attention over pair rows at N = 768 (q, k, v bf16
-[768, 4, 768, 32], fp32 bias [4, 768, 768], row-wise key mask); for N > 1 every rank owns a
-block of 768 more pair rows of the same problem (rows are independent, so there is no
-data-path collective; bias and mask are broadcast once, untimed) and the line reports
-``"scaling": "weak"``.  Rank 0 prints ONE JSON line.
+One "step" is one pass of the operator over a batch of CALLS_PER_STEP (16) attention problems of
+the workload's shape, issued back to back on one stream (so that a step is long enough for the
+clock sampler to see it); ``ms_per_call`` is the step time divided by 16.  At N = 1 the workload
+is grid / triangle self-attention over pair rows at N = 768 (q, k, v bf16 [768, 4, 768, 32],
+fp32 bias [4, 768, 768], row-wise key mask); the line also carries a ``configs`` object with the
+other four benchmark configurations.  For N > 1 every rank owns 768 more pair rows of the same
+problem (rows are independent, so the headline has no data-path collective; ``"scaling":
+"weak"``) and the line gains a ``row_sharded`` object: the N = 2048 fp8 configuration split by
+pair row over the ranks, bias and mask broadcast with NCCL, outputs all-gathered in pieces on a
+side stream, with both scaling efficiencies and the link-rate floor of the gather.  Rank 0
+prints ONE JSON line.
 
 ``--impl reference`` times the CPU restatement of the reference operator (oracle/, all host
-threads) on a bounded row sample of the same workload; the reference's own libxsmm build is not
-available on this machine.
+threads) on the same workload - every pair row when a step costs at most a few seconds, else a
+bounded row sample; the reference's own libxsmm build is not available on this machine.
 """
 from __future__ import annotations
 
@@ -32,6 +37,8 @@ sys.path.insert(0, ROOT)
 METRIC = "biased_attention_tflops"
 UNIT = "TFLOP/s"
 NOMINAL_BF16_TFLOPS = 2250.0
+CALLS_PER_STEP = 16
+NVLINK_GBS_PER_DIRECTION = 900.0   # nominal, per GPU; the measured peer-copy rate on this pool is 770
 
 
 def load_peaks():
@@ -98,25 +105,66 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU arm
-def time_cpu_port(inp, shape, target_s: float, max_rows: int):
-    """Times the C restatement on a row sample sized for about ``target_s`` seconds."""
-    from oracle import attention_oracle as O
+def _cpu_inputs(O, name, rows):
+    c = O.CONFIGS[name]
+    inp = O.make_inputs(name, rows=rows)
+    if c.get("fp8"):   # the reference has no fp8 path: its bf16 operator on de-quantised inputs
+        inp["q"] = (inp["q"].float() * inp["q_scale"].view(1, -1, 1, 1)).to(torch.bfloat16)
+        inp["k"] = (inp["k"].float() * inp["k_scale"].view(1, -1, 1, 1)).to(torch.bfloat16)
+    return inp
+
+
+def _run_port(O, inp, rows):
+    t0 = time.time()
+    O.ref_semantics(inp["q"][:rows], inp["k"][:rows], inp["v"][:rows], inp["mask"][:rows], inp["bias"])
+    return time.time() - t0
+
+
+def rows_for_budget(O, inp, max_rows, target_s):
+    """Pair rows whose CPU time is about ``target_s`` seconds (all of them when they fit)."""
+    probe = min(2, max_rows)
+    _run_port(O, inp, probe)              # warm: builds / loads the library, touches memory
+    t = _run_port(O, inp, probe)
+    return int(max(probe, min(max_rows, target_s / max(t, 1e-4) * probe)))
+
+
+def time_cpu_port(O, name, shape, target_s):
+    """The C restatement of the reference operator on all host threads: one call over as many
+    pair rows as fit ``target_s`` seconds."""
     B1, B2, S, D = shape
-
-    def run(rows):
-        t0 = time.time()
-        O.ref_semantics(inp["q"][:rows], inp["k"][:rows], inp["v"][:rows], inp["mask"][:rows],
-                        inp["bias"])
-        return time.time() - t0
-
-    probe_rows = min(2, max_rows)
-    run(probe_rows)                       # warm: builds / loads the library, touches memory
-    t = run(probe_rows)
-    rows = int(max(probe_rows, min(max_rows, target_s / max(t, 1e-4) * probe_rows)))
-    secs = run(rows)
+    probe_inp = _cpu_inputs(O, name, min(B1, 2))
+    rows = rows_for_budget(O, probe_inp, B1, target_s)
+    inp = _cpu_inputs(O, name, rows)
+    secs = _run_port(O, inp, rows)
     flops = O.attention_flops(rows, B2, S, S, D)
     return {"value": flops / secs / 1e12, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
-            "sample": f"{rows} of {B1} pair rows, one call, {secs:.2f} s", "rows": rows, "secs": secs}
+            "sample": f"{rows} of {B1} pair rows, one call, {secs:.2f} s"}
+
+
+def time_cpu_torch_bf16(O, name, shape, target_s):
+    """The comparison baseline the reference's own example prints as "Torch ms"
+    (examples/dot_product_attention.py:20-43, :150-156): the PyTorch restatement in bf16 on the
+    host cores."""
+    B1, B2, S, D = shape
+    rows = min(B1, 2)
+    inp = _cpu_inputs(O, name, rows)
+
+    def run(r):
+        t0 = time.time()
+        O.torch_baseline_bf16(inp["q"][:r], inp["k"][:r], inp["v"][:r], inp["mask"][:r], inp["bias"])
+        return time.time() - t0
+
+    run(rows)
+    t = run(rows)
+    want = int(max(rows, min(B1, target_s / max(t, 1e-4) * rows)))
+    if want != rows:
+        rows = want
+        inp = _cpu_inputs(O, name, rows)
+    secs = run(rows)
+    return {"value": O.attention_flops(rows, B2, S, S, D) / secs / 1e12, "unit": UNIT,
+            "cores": torch.get_num_threads(), "kind": "port",
+            "what": "PyTorch bf16 restatement of the operator on CPU (the reference example's own baseline)",
+            "sample": f"{rows} of {B1} pair rows, one call, {secs:.2f} s"}
 
 
 def reference_arm(args, world, rank):
@@ -125,43 +173,39 @@ def reference_arm(args, world, rank):
     from oracle import attention_oracle as O
     name = args.workload
     c = O.CONFIGS[name]
-    shape = (c["B1"], c["B2"], c["S"], c["D"])
-    sample_rows = min(c["B1"], 16)
-    inp = O.make_inputs(name, rows=sample_rows)
-    if c.get("fp8"):   # the reference has no fp8 path: time its bf16 operator on de-quantised inputs
-        inp["q"] = (inp["q"].float() * inp["q_scale"].view(1, -1, 1, 1)).to(torch.bfloat16)
-        inp["k"] = (inp["k"].float() * inp["k_scale"].view(1, -1, 1, 1)).to(torch.bfloat16)
-    # size one step for roughly (120 s / steps) of CPU work
-    budget = max(1.0, min(10.0, 120.0 / max(1, args.steps + args.warmup)))
-    first = time_cpu_port(inp, shape, budget, sample_rows)
-    rows = first["rows"]
+    B1, B2, S, D = c["B1"], c["B2"], c["S"], c["D"]
+    n_steps = max(1, args.steps + args.warmup)
+    # one step = the whole workload when that costs at most 5 s and the run stays within ~3 minutes
+    probe_inp = _cpu_inputs(O, name, min(B1, 2))
+    per_step_s = min(5.0, 180.0 / n_steps)
+    rows = rows_for_budget(O, probe_inp, B1, per_step_s)
+    inp = _cpu_inputs(O, name, rows)
     times = []
     for i in range(args.warmup + args.steps):
-        t0 = time.time()
-        O.ref_semantics(inp["q"][:rows], inp["k"][:rows], inp["v"][:rows], inp["mask"][:rows], inp["bias"])
+        secs = _run_port(O, inp, rows)
         if i >= args.warmup:
-            times.append(time.time() - t0)
+            times.append(secs)
     ms = 1e3 * sum(times) / len(times)
-    flops = O.attention_flops(rows, c["B2"], c["S"], c["S"], c["D"])
-    value = flops / (ms / 1e3) / 1e12
-    sample = f"{rows} of {c['B1']} pair rows per step"
+    value = O.attention_flops(rows, B2, S, S, D) / (ms / 1e3) / 1e12
+    sample = f"{rows} of {B1} pair rows per step" + (" (the whole workload)" if rows == B1 else "")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(name, c, world, sample_rows=rows),
+        "config": workload_config(name, c, world),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "note": "CPU restatement of the reference operator (oracle/ref_semantics.c, pthreads); "
-                "the reference's libxsmm build is unavailable on this machine",
+        "note": "CPU restatement of the reference operator (oracle/ref_semantics.c: plain C, "
+                "auto-vectorised, pthreads) - a port, not the reference's libxsmm AMX/AVX-512 JIT "
+                "kernels, which cannot be built on this machine and would be several times faster",
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(name, c, world, sample_rows=None):
-    cfg = {
+def workload_config(name, c, world):
+    return {
         "workload": f"{name}: biased key-masked attention, q/k/v [{c['B1']},{c['B2']},{c['S']},{c['D']}]"
                     f" {'fp8-e4m3 q/k' if c.get('fp8') else 'bf16'}, bias {str(c['bias_dtype']).split('.')[-1]}"
                     f" [{c['B2']},{c['S']},{c['S']}], mask {c['mask']}",
@@ -169,24 +213,179 @@ def workload_config(name, c, world, sample_rows=None):
         "parallelism": f"rows{world}" if world > 1 else "single",
         "cache": "inputs larger than L2 (no flush)" if name in ("cfg2", "cfg5") else "L2 flushed between steps",
     }
-    if sample_rows is not None:
-        cfg["cpu_sample_rows"] = sample_rows
-    return cfg
 
 
 # --------------------------------------------------------------------------- GPU arm
+def device_inputs(O, name, rows, dev, seed):
+    """Seeded synthetic inputs of a configuration, generated on the device."""
+    c = dict(O.CONFIGS[name])
+    B1, B2, S, D = rows, c["B2"], c["S"], c["D"]
+    g = torch.Generator(device=dev).manual_seed(seed)
+    qf = torch.randn(B1, B2, S, D, generator=g, device=dev)
+    kf = torch.randn(B1, B2, S, D, generator=g, device=dev)
+    v = torch.randn(B1, B2, S, D, generator=g, device=dev).to(torch.bfloat16)
+    if c.get("fp8"):
+        q, q_scale = O.quantize_e4m3_per_head(qf)
+        k, k_scale = O.quantize_e4m3_per_head(kf)
+    else:
+        q, k, q_scale, k_scale = qf.to(torch.bfloat16), kf.to(torch.bfloat16), None, None
+    del qf, kf
+    gb = torch.Generator(device=dev).manual_seed(0)
+    bias = (torch.randn(B2, S, S, generator=gb, device=dev) * c["bias_std"]).to(c["bias_dtype"])
+    if c["mask"].startswith("tail"):
+        mask = torch.ones(B1, S, dtype=torch.bool, device=dev)
+        mask[:, S - int(c["mask"][4:]):] = False
+    else:
+        mask = torch.rand(B1, S, generator=g, device=dev) >= 0.05
+    return dict(q=q, k=k, v=v, bias=bias, mask=mask, q_scale=q_scale, k_scale=k_scale)
+
+
+def event_ms(fn, reps, before=None):
+    """Milliseconds of each of ``reps`` calls of fn(), CUDA events on the current stream."""
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for e0, e1 in evs:
+        if before is not None:
+            before()
+        e0.record()
+        fn()
+        e1.record()
+    torch.cuda.synchronize()
+    return [e0.elapsed_time(e1) for e0, e1 in evs]
+
+
+def config_table(O, dev, peaks, flush, skip):
+    """ms per call, TFLOP/s and roofline fraction of the other benchmark configurations (kernel
+    calls on device-resident inputs, L2 flushed between calls for the ones that fit in it)."""
+    from af3_kernels_b200.dpa import dot_product_attention
+    table = {}
+    for name in ("cfg1", "cfg3", "cfg4", "cfg5"):
+        if name == skip:
+            continue
+        c = O.CONFIGS[name]
+        B1, B2, S, D = c["B1"], c["B2"], c["S"], c["D"]
+        t = device_inputs(O, name, B1, dev, seed=2000)
+        kw = dict(q_scale=t["q_scale"], k_scale=t["k_scale"]) if c.get("fp8") else {}
+        call = lambda: dot_product_attention(t["q"], t["k"], t["v"], t["mask"], t["bias"], **kw)
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        small = name != "cfg5"
+        ms = statistics.median(event_ms(call, 20 if small else 5, before=flush.zero_ if small else None))
+        flops = O.attention_flops(B1, B2, S, S, D)
+        nbytes = O.attention_bytes(B1, B2, S, S, D, qk_bytes=1 if c.get("fp8") else 2,
+                                   bias_bytes=4 if c["bias_dtype"] == torch.float32 else 2)
+        tf, gbs = flops / ms / 1e9, nbytes / ms / 1e6
+        # the roofline that binds by the definition "slower of flops at tensor peak and bytes at HBM rate"
+        hbm_bound = nbytes / peaks["hbm_gbs"] / 1e9 > flops / peaks["bf16_tflops"] / 1e12
+        table[name] = {
+            "workload": workload_config(name, c, 1)["workload"], "ms": ms, "tflops": tf, "gbs": gbs,
+            "bound": "hbm" if hbm_bound else "tensor",
+            "frac": gbs / peaks["hbm_gbs"] if hbm_bound else tf / peaks["bf16_tflops"],
+            "cache": "L2 flushed between calls" if small else "inputs larger than L2",
+        }
+        del t
+        torch.cuda.empty_cache()
+    return table
+
+
+def row_sharded_report(args, O, dev, world, rank):
+    """The N = 2048 fp8 configuration split by pair row over the ranks (reference:
+    src/af3_kernels/Attention.py:145-198): bias and mask broadcast from rank 0 with NCCL, every
+    rank computes its row block, the blocks are all-gathered in pieces on a side stream."""
+    import torch.distributed as dist
+    from af3_kernels_b200.dpa import dot_product_attention
+    from af3_kernels_b200.distributed import RowShardedAttention, row_partition
+
+    c = O.CONFIGS["cfg5"]
+    rows = args.sharded_rows or c["B1"]
+    B2, S, D = c["B2"], c["S"], c["D"]
+    t = device_inputs(O, "cfg5", rows, dev, seed=5000)      # same seed: identical on every rank
+    kw = dict(q_scale=t["q_scale"], k_scale=t["k_scale"])
+    bias = t["bias"] if rank == 0 else torch.zeros_like(t["bias"])
+    mask_u8 = (t["mask"] if rank == 0 else torch.zeros_like(t["mask"])).view(torch.uint8)
+
+    def max_over_ranks(x):
+        v = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        return v.item()
+
+    sharder = RowShardedAttention(comm_split=4)
+    # replicated operands: one NCCL broadcast each into every GPU's own memory (first one warms NCCL up)
+    sharder.broadcast_shared(bias.clone(), mask_u8.clone())
+    torch.cuda.synchronize()
+    dist.barrier()
+    bcast_ms = max_over_ranks(event_ms(lambda: sharder.broadcast_shared(bias, mask_u8), 1)[0])
+    mask = mask_u8.view(torch.bool)
+
+    # T1: the whole problem on one GPU (every rank runs it; rank 0's figure is reported)
+    single = None
+    for _ in range(2):
+        single = dot_product_attention(t["q"], t["k"], t["v"], mask, bias, **kw)
+    torch.cuda.synchronize()
+    t1 = statistics.median(event_ms(lambda: dot_product_attention(t["q"], t["k"], t["v"], mask, bias, **kw), 5))
+    t1_all = torch.tensor([t1], dtype=torch.float64, device=dev)
+    dist.broadcast(t1_all, src=0)
+    t1_ms = t1_all.item()
+
+    b, e, split = row_partition(rows, world, rank)
+    ql, kl, vl, ml = t["q"][b:e], t["k"][b:e], t["v"][b:e], mask[b:e]
+    local = lambda: dot_product_attention(ql, kl, vl, ml, bias, **kw)
+    for _ in range(2):
+        local()
+    torch.cuda.synchronize()
+    dist.barrier()
+    kernel_ms = max_over_ranks(statistics.median(event_ms(local, 5)))
+
+    fn = lambda q_, k_, v_, m_, b_: dot_product_attention(q_, k_, v_, m_, b_, **kw)
+    sharder.attention_fn = fn
+    gathered = sharder.forward(ql, kl, vl, ml, bias, rows)          # warm-up (NCCL channels, buffers)
+    torch.cuda.synchronize()
+    equal = bool(torch.equal(gathered, single))
+    eq = torch.tensor([1 if equal else 0], dtype=torch.int32, device=dev)
+    dist.all_reduce(eq, op=dist.ReduceOp.MIN)
+    del gathered
+    times = []
+    for _ in range(3):
+        dist.barrier()
+        torch.cuda.synchronize()
+        times.append(event_ms(lambda: sharder.forward(ql, kl, vl, ml, bias, rows), 1)[0])
+    total_ms = max_over_ranks(statistics.median(times))
+
+    out_bytes = rows * B2 * S * D * 2
+    inbound = out_bytes * (world - 1) / world
+    floor_ms = inbound / (NVLINK_GBS_PER_DIRECTION * 1e9) * 1e3
+    flops = O.attention_flops(rows, B2, S, S, D)
+    return {
+        "workload": f"cfg5: q/k fp8-e4m3 [{rows},{B2},{S},{D}] + per-head scales, v bf16, bias bf16 "
+                    f"[{B2},{S},{S}], mask rand05; pair rows split {split} per rank",
+        "t1_ms": t1_ms, "t1_tflops": flops / t1_ms / 1e9,
+        "kernel_ms_max_rank": kernel_ms, "E1": t1_ms / (world * kernel_ms),
+        "bcast_ms": bcast_ms, "bcast_bytes": bias.numel() * 2 + mask_u8.numel(),
+        "total_ms": total_ms, "total_tflops": flops / total_ms / 1e9,
+        "E2": t1_ms / (world * total_ms), "E2_with_bcast": t1_ms / (world * (total_ms + bcast_ms)),
+        "gather_inbound_bytes_per_gpu": inbound, "gather_floor_ms": floor_ms,
+        "gather_floor_basis": f"{NVLINK_GBS_PER_DIRECTION:.0f} GB/s per direction per GPU (nominal NVLink 5)",
+        "comm_split": sharder.comm_split, "sharded_equals_single": bool(eq.item() == 1),
+        "definitions": "E1 = t1 / (N * slowest rank's kernel on its row block); E2 = t1 / (N * time of "
+                       "RowShardedAttention.forward: kernel pieces + chunked NCCL all-gather on a side stream)",
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2",
                     choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "grid_block", "pair_bias"])
     ap.add_argument("--rows", type=int, default=0, help="override pair rows per GPU (debugging)")
+    ap.add_argument("--sharded-rows", type=int, default=0, help="override the row count of the row-sharded part")
+    ap.add_argument("--calls-per-step", type=int, default=CALLS_PER_STEP)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="skip the table of the other configurations")
     ap.add_argument("--kernel-only", action="store_true",
-                    help="only warm-up + timed steps with a bf16 bias (for ncu captures): no e2e, no CPU leg")
+                    help="only warm-up + timed calls with a bf16 bias (for ncu captures): no e2e, no CPU leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -225,24 +424,9 @@ def main():
     B1, B2, S, D = c["B1"], c["B2"], c["S"], c["D"]
     fp8 = bool(c.get("fp8"))
 
-    # ---- inputs: every rank owns B1 pair rows; bias (and the mask pattern) come from rank 0
-    g = torch.Generator(device=dev).manual_seed(1000 + rank)
-    qf = torch.randn(B1, B2, S, D, generator=g, device=dev)
-    kf = torch.randn(B1, B2, S, D, generator=g, device=dev)
-    v = torch.randn(B1, B2, S, D, generator=g, device=dev).to(torch.bfloat16)
-    if fp8:
-        q, q_scale = O.quantize_e4m3_per_head(qf)
-        k, k_scale = O.quantize_e4m3_per_head(kf)
-    else:
-        q, k, q_scale, k_scale = qf.to(torch.bfloat16), kf.to(torch.bfloat16), None, None
-    del qf, kf
-    gb = torch.Generator(device=dev).manual_seed(0)
-    bias = (torch.randn(B2, S, S, generator=gb, device=dev) * c["bias_std"]).to(c["bias_dtype"])
-    if c["mask"].startswith("tail"):
-        mask = torch.ones(B1, S, dtype=torch.bool, device=dev)
-        mask[:, S - int(c["mask"][4:]):] = False
-    else:
-        mask = torch.rand(B1, S, generator=g, device=dev) >= 0.05
+    # ---- inputs: every rank owns B1 pair rows of its own; the bias comes from rank 0
+    t = device_inputs(O, name, B1, dev, seed=1000 + rank)
+    q, k, v, mask, bias, q_scale, k_scale = (t[n] for n in ("q", "k", "v", "mask", "bias", "q_scale", "k_scale"))
     if world > 1:
         dist.broadcast(bias, src=0)
         if fp8:
@@ -250,14 +434,15 @@ def main():
             dist.broadcast(k_scale, src=0)
     kw = dict(q_scale=q_scale, k_scale=k_scale) if fp8 else {}
 
-    flush = None
-    if name not in ("cfg2", "cfg5"):   # small workloads fit in L2: flush it between steps
-        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    small = name not in ("cfg2", "cfg5")     # small workloads fit in L2: flush it between calls
+    cps = 1 if args.kernel_only else max(1, args.calls_per_step)
 
     def step():
-        if flush is not None:
-            flush.zero_()
-        return dot_product_attention_cpp(q, k, v, mask, bias, **kw)
+        for _ in range(cps):
+            if small:
+                flush.zero_()
+            dot_product_attention_cpp(q, k, v, mask, bias, **kw)
 
     def sync_all():
         if world > 1:
@@ -269,29 +454,21 @@ def main():
         bias = bias.to(torch.bfloat16)
     for _ in range(args.warmup):
         step()
-    launches_per_step = lib.af3k_last_launch_count()
+    launches_per_call = lib.af3k_last_launch_count()
     sync_all()
     sampler = ClockSampler(local_rank)
     sampler.start()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-           for _ in range(args.steps)]
-    for e0, e1 in evs:
-        if flush is not None:
-            flush.zero_()
-        e0.record()
-        dot_product_attention_cpp(q, k, v, mask, bias, **kw)
-        e1.record()
+    step_ms = event_ms(step, args.steps)
     sync_all()
     clocks = sampler.stop()
-    step_ms = [e0.elapsed_time(e1) for e0, e1 in evs]
     total_ms = torch.tensor([sum(step_ms)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
     ms_per_step = total_ms.item() / args.steps
     status = read_status(dev)
 
-    flops_rank = O.attention_flops(B1, B2, S, S, D)
-    value = world * flops_rank / (ms_per_step / 1e3) / 1e12
+    flops_call = O.attention_flops(B1, B2, S, S, D)
+    value = world * cps * flops_call / (ms_per_step / 1e3) / 1e12
 
     if args.kernel_only:
         if rank == 0:
@@ -305,9 +482,9 @@ def main():
         return
 
     # ---- end to end through the reference-facing operator with HOST buffers (every rank)
-    host = {n: t.cpu().pin_memory() for n, t in (("q", q), ("k", k), ("v", v), ("bias", bias), ("mask", mask))}
+    host = {n: x.cpu().pin_memory() for n, x in (("q", q), ("k", k), ("v", v), ("bias", bias), ("mask", mask))}
     out_host = torch.empty((B1, B2, S, D), dtype=torch.bfloat16).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    h2d = sum(x.numel() * x.element_size() for x in host.values())
     d2h = out_host.numel() * out_host.element_size()
     e2e_steps = max(3, min(args.steps, 10))
 
@@ -328,9 +505,18 @@ def main():
     if world > 1:
         dist.all_reduce(e2e_total, op=dist.ReduceOp.MAX)
     e2e_ms = e2e_total.item() / e2e_steps
-    e2e = {"value": world * flops_rank / (e2e_ms / 1e3) / 1e12, "unit": UNIT,
+    e2e = {"value": world * flops_call / (e2e_ms / 1e3) / 1e12, "unit": UNIT,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-           "steps": e2e_steps}
+           "steps": e2e_steps, "calls_per_step": 1,
+           "what": "dot_product_attention_cpp on pinned host tensors: H2D of q/k/v/bias/mask, kernel, "
+                   "D2H of the result inside the timed region, every step"}
+    del host, out_host
+
+    row_sharded = None
+    if world > 1:
+        del q, k, v, t
+        torch.cuda.empty_cache()
+        row_sharded = row_sharded_report(args, O, dev, world, rank)
 
     if rank != 0:
         if world > 1:
@@ -338,54 +524,58 @@ def main():
             dist.destroy_process_group()
         return
 
+    if world > 1:      # the headline inputs were released for the row-sharded part
+        t = device_inputs(O, name, B1, dev, seed=1000 + rank)
+        q, k, v, mask = t["q"], t["k"], t["v"], t["mask"]
+
     # ---- roofline of the dominant kernel: the attention kernel alone (bias already bf16, so the
     # staging pre-pass does not run), CUDA events around each launch on the launching stream
     peaks = load_peaks()
     bias16 = bias.to(torch.bfloat16)
+    kcall = lambda: dot_product_attention(q, k, v, mask, bias16, **kw)
     for _ in range(3):
-        dot_product_attention(q, k, v, mask, bias16, **kw)
+        kcall()
     torch.cuda.synchronize()
-    kevs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-            for _ in range(min(args.steps, 50))]
-    for e0, e1 in kevs:
-        if flush is not None:
-            flush.zero_()
-        e0.record()
-        dot_product_attention(q, k, v, mask, bias16, **kw)
-        e1.record()
-    torch.cuda.synchronize()
-    kernel_ms = sum(e0.elapsed_time(e1) for e0, e1 in kevs) / len(kevs)
-    achieved = flops_rank / (kernel_ms / 1e3) / 1e12
+    kms = event_ms(kcall, max(20, min(args.steps * cps, 100)), before=flush.zero_ if small else None)
+    kernel_ms = sum(kms) / len(kms)
+    achieved = flops_call / (kernel_ms / 1e3) / 1e12
     alg_bytes = O.attention_bytes(B1, B2, S, S, D, qk_bytes=1 if fp8 else 2, bias_bytes=2)
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
         "frac": achieved / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (bf16 burst)",
-        "kernel": "attention_kernel", "kernel_ms": kernel_ms,
-        "flops_per_launch": flops_rank, "algorithmic_bytes_per_launch": alg_bytes,
+        "kernel": "attention_kernel", "kernel_ms": kernel_ms, "kernel_ms_min": min(kms),
+        "flops_per_launch": flops_call, "algorithmic_bytes_per_launch": alg_bytes,
         "frac_of_nominal_2250": achieved / NOMINAL_BF16_TFLOPS,
         "hbm_gbs_achieved": alg_bytes / (kernel_ms / 1e3) / 1e9,
         "traffic": TRAFFIC_BYTES.get(name),
     }
 
-    cpu_baseline = None
+    configs = None
+    if world == 1 and not args.no_configs:
+        del q, k, v, t
+        torch.cuda.empty_cache()
+        configs = config_table(O, dev, peaks, flush, skip=name)
+
+    cpu_baseline = cpu_torch = None
     if not args.no_cpu_baseline and world == 1:
-        cpu_in = {n: host[n] for n in ("q", "k", "v", "bias", "mask")}
-        if fp8:
-            cpu_in["q"] = (host["q"].float() * q_scale.cpu().view(1, -1, 1, 1)).to(torch.bfloat16)
-            cpu_in["k"] = (host["k"].float() * k_scale.cpu().view(1, -1, 1, 1)).to(torch.bfloat16)
-        cb = time_cpu_port(cpu_in, (B1, B2, S, D), target_s=12.0, max_rows=B1)
-        cpu_baseline = {kk: cb[kk] for kk in ("value", "unit", "cores", "kind", "sample")}
+        cpu_baseline = time_cpu_port(O, name, (B1, B2, S, D), target_s=12.0)
+        cpu_torch = time_cpu_torch_bf16(O, name, (B1, B2, S, D), target_s=6.0)
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8+bf16" if fp8 else "bf16",
         "data": "synthetic (seeded normal q/k/v/bias, Bernoulli or tail key mask)",
-        "config": workload_config(name, c, world),
-        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-        "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+        "config": dict(workload_config(name, c, world), calls_per_step=cps),
+        "calls_per_step": cps, "ms_per_call": ms_per_step / cps,
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "cpu_baseline_torch_bf16": cpu_torch, "e2e": e2e,
+        "gpu_launches": launches_per_call * cps * args.steps, "clocks": clocks,
         "device_status": status,
     }
+    if configs is not None:
+        line["configs"] = configs
+    if row_sharded is not None:
+        line["row_sharded"] = row_sharded
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

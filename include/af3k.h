@@ -62,6 +62,9 @@ typedef struct af3k_attention_desc {
   int32_t bias_dtype;     /* AF3K_BF16 or AF3K_F32 */
   float softmax_scale;    /* the reference uses 1/sqrt(D) */
   int32_t rows_per_item;  /* 0 = choose; else requested pair rows per staged bias tile (1..8, clamped to what fits, at most 4) */
+  int32_t bias_prescaled; /* fp8 q/k only: 1 = `bias` is the output of af3k_stage_bias for these scales (already divided
+                             by the head's logit scale); the tensor core adds it and no staging pass runs.  0 otherwise. */
+  int32_t reserved_;      /* must be 0 */
 } af3k_attention_desc;
 
 /* Library / ABI version (major * 1000 + minor). */
@@ -79,6 +82,20 @@ const char* af3k_last_error_detail(void);
  * cannot address (AF3K_ERR_WORKSPACE without it); with fp8 q/k it is optional and selects the
  * faster kernel, in which the tensor core adds the (pre-scaled) bias. */
 size_t af3k_dot_product_attention_workspace(const af3k_attention_desc* desc, const void* bias);
+
+/* The bias staging pass on its own, for callers that use one bias in many attention calls (the
+ * diffusion transformer applies the same pair bias in every denoising step): converts `bias`
+ * (bf16 or fp32, any row pitch) into `staged`, a bf16 [B2, Sq, round_up(Sk, 8)] array that
+ * af3k_dot_product_attention reads in place, so that later calls launch one kernel instead of
+ * two.  Pass `staged` as the bias of those calls with bias_dtype = AF3K_BF16 and bias_stride =
+ * {Sq * round_up(Sk, 8), round_up(Sk, 8)}.  With fp8 q/k (q_scale / k_scale non-NULL) every value
+ * is also divided by softmax_scale * q_scale[h] * k_scale[h]; set desc.bias_prescaled = 1 in the
+ * calls that use such a copy.  staged_bytes must be at least
+ * af3k_dot_product_attention_workspace()'s figure for an fp32 bias of this shape (B2 * Sq *
+ * round_up(Sk, 8) * 2).  Stands in for the cast the reference's wrapper makes on every call
+ * (`bias = bias.to(q.dtype)`, src/af3_kernels/__init__.py:48). */
+int af3k_stage_bias(const af3k_attention_desc* desc, const void* bias, const float* q_scale,
+                    const float* k_scale, void* staged, size_t staged_bytes, void* stream);
 
 /* out = softmax(scale * q k^T + bias, key-masked) v
  *
@@ -115,7 +132,10 @@ int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, c
  * AF3K_ERR_SCRATCH_LIMIT and nothing is launched.
  *
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
- * that device current); make that first call outside any stream capture.  All calls on a device
+ * that device current); make that first call outside any stream capture.  The address is kept
+ * for the life of the process: after a cudaDeviceReset of that device it is stale and this entry
+ * point must not be used again in the process.  With fp8 q/k the staging copy is optional; when
+ * it does not fit the array it is left out and the slower kernel variant runs (no error).  All calls on a device
  * share the one array: two calls whose kernels can overlap on the GPU (different streams) race
  * on it, so keep them on one stream or order them with events.  Nothing in the array has to be
  * cleared between calls; each call rewrites every entry it reads.

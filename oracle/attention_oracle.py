@@ -65,6 +65,20 @@ def oracle_fp32(q, k, v, mask, bias, q_scale=None, k_scale=None) -> torch.Tensor
     return torch.matmul(weights, vf)
 
 
+def torch_baseline_bf16(q, k, v, mask, bias) -> torch.Tensor:
+    """The same function evaluated in the inputs' own dtype (bf16), as the reference's example
+    runs it for its "Torch ms" timing (examples/dot_product_attention.py:20-43, :139-148).  Used
+    as a timed CPU baseline only."""
+    scaling = q.size(-1) ** -0.5
+    logits = torch.matmul(q * scaling, k.transpose(-1, -2))
+    logits = logits + bias.to(logits.dtype).reshape(1, q.shape[1], q.shape[2], k.shape[2])
+    m = lift_mask(mask)
+    if m is not None:
+        logits.masked_fill_(~m, -1e9)
+    weights = torch.softmax(logits, dim=-1)
+    return torch.matmul(weights, v)
+
+
 # ----------------------------------------------------------------------------- O2
 def build_c_oracle(force: bool = False) -> str:
     src = os.path.join(_HERE, "ref_semantics.c")

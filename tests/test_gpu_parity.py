@@ -129,7 +129,8 @@ def test_fp8_both_kernel_variants(cuda_device):
         k, ks = O.quantize_e4m3_per_head(kf)
         ref = O.oracle_fp32(q, k, v, mask, bias, q_scale=qs, k_scale=ks)
         for use_ws in (True, False):
-            out = _run(cuda_device, q, k, v, mask, bias, q_scale=qs, k_scale=ks, use_workspace=use_ws)
+            out = _run(cuda_device, q, k, v, mask, bias, q_scale=qs, k_scale=ks, use_workspace=use_ws,
+                       cache_bias=False)
             st = O.error_stats(out, ref)
             assert st["nan"] == 0 and st["max_abs"] <= FP8_MAX_ABS, (amp, use_ws, st)
             uniform = v[1].float().mean(dim=1, keepdim=True).expand(B2, S, D)
@@ -296,11 +297,48 @@ def test_bounded_wait_reports_instead_of_hanging(cuda_device):
 def test_launch_count(cuda_device):
     lib = _capi.load()
     q = torch.randn(1, 1, 64, 32, device=cuda_device).to(torch.bfloat16)
-    dot_product_attention(q, q, q, None, torch.zeros(1, 64, 64, device=cuda_device))
+    dot_product_attention(q, q, q, None, torch.zeros(1, 64, 64, device=cuda_device), cache_bias=False)
     assert lib.af3k_last_launch_count() == 2          # fp32 bias: staging pre-pass + attention
     dot_product_attention(q, q, q, None, torch.zeros(1, 64, 64, device=cuda_device, dtype=torch.bfloat16))
     assert lib.af3k_last_launch_count() == 1
     assert read_status(cuda_device)[0] == 0
+
+
+def test_staged_bias_is_reused_and_follows_in_place_updates(cuda_device):
+    """A bias that needs the staging pass is staged once per tensor object and version: the second
+    call with the same tensor launches one kernel, gives the same bits as a call that stages
+    inside, and an in-place update of the bias is seen by the next call.  Same for fp8 q/k, whose
+    copy also depends on the scales."""
+    dev = cuda_device
+    lib = _capi.load()
+    g = torch.Generator().manual_seed(5)
+    B1, B2, S, D = 3, 2, 200, 32
+    q, k, v = (torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16).to(dev) for _ in range(3))
+    bias = torch.randn(B2, S, S, generator=g).to(dev)
+    mask = (torch.rand(B1, S, generator=g) >= 0.1).to(dev)
+    inside = dot_product_attention(q, k, v, mask, bias, cache_bias=False, check_status=True)
+    first = dot_product_attention(q, k, v, mask, bias, check_status=True)
+    second = dot_product_attention(q, k, v, mask, bias, check_status=True)
+    assert lib.af3k_last_launch_count() == 1
+    assert torch.equal(first, inside) and torch.equal(second, inside)
+    bias.mul_(-1.0)                                   # same object, new version
+    flipped = dot_product_attention(q, k, v, mask, bias, check_status=True)
+    assert torch.equal(flipped, dot_product_attention(q, k, v, mask, bias, cache_bias=False))
+    assert not torch.equal(flipped, inside)
+    # explicit handle
+    from af3_kernels_b200.dpa import stage_bias
+    handle = stage_bias(bias, B2, S, S)
+    assert torch.equal(dot_product_attention(q, k, v, mask, handle, check_status=True), flipped)
+    # fp8 q/k
+    q8, qs = O.quantize_e4m3_per_head(q.float().cpu())
+    k8, ks = O.quantize_e4m3_per_head(k.float().cpu())
+    q8, k8, qs, ks = q8.to(dev), k8.to(dev), qs.to(dev), ks.to(dev)
+    b16 = bias.to(torch.bfloat16)
+    ref8 = dot_product_attention(q8, k8, v, mask, b16, q_scale=qs, k_scale=ks, cache_bias=False, check_status=True)
+    for _ in range(2):
+        got = dot_product_attention(q8, k8, v, mask, b16, q_scale=qs, k_scale=ks, check_status=True)
+        assert torch.equal(got, ref8)
+    assert lib.af3k_last_launch_count() == 1
 
 
 def test_debug_dump_shows_the_tensor_core_stages(cuda_device):
