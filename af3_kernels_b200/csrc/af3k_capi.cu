@@ -45,6 +45,17 @@ long long wait_limit_cycles() {
   return v;
 }
 
+// Experiment switch: which exponential formulation the tensor-core-bias kernel uses (see kExp in
+// attn_sm100.cuh).  Read once from AF3K_EXP_MODE.
+int exp_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = std::getenv("AF3K_EXP_MODE");
+    mode = e ? std::atoi(e) : 0;
+  }
+  return mode;
+}
+
 PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
   static std::once_flag once;
@@ -91,7 +102,12 @@ int device_info(DeviceInfo** out) {
     if ((e = cudaFuncSetAttribute(attention_kernel<false, false>, attr, dyn)) != cudaSuccess ||
         (e = cudaFuncSetAttribute(attention_kernel<false, true>, attr, dyn)) != cudaSuccess ||
         (e = cudaFuncSetAttribute(attention_kernel<true, false>, attr, dyn)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(attention_kernel<true, true>, attr, dyn)) != cudaSuccess)
+        (e = cudaFuncSetAttribute(attention_kernel<true, true>, attr, dyn)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(attention_kernel<false, true, 2>, attr, dyn)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(attention_kernel<false, true, 3>, attr, dyn)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(attention_kernel<false, true, 4>, attr, dyn)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(attention_kernel<false, true, 5>, attr, dyn)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(attention_kernel<false, true, 8>, attr, dyn)) != cudaSuccess)
       return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize)", e);
     if ((e = cudaFuncSetAttribute(pair_bias_kernel_t<float>, attr, PbTile<float>::kSmemBytes)) != cudaSuccess ||
         (e = cudaFuncSetAttribute(pair_bias_kernel_t<__nv_bfloat16>, attr, PbTile<__nv_bfloat16>::kSmemBytes)) !=
@@ -162,7 +178,9 @@ struct Plan {
 };
 
 // Picks rows-per-item G and the K/V ring depth from a cost model of one CTA's time (below).
-int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
+// allow_q_split: the kernel variant that will run supports query-tile streams (every variant in
+// which the tensor core adds the bias).
+int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan, bool allow_q_split = true) {
   AttnParams& p = plan->p;
   std::memset(&p, 0, sizeof(p));
   const int es = d.qk_dtype == AF3K_FP8_E4M3 ? 1 : 2;
@@ -196,37 +214,43 @@ int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan) {
   for (int g = 1; g <= g_max; ++g) {
     if (g_req != 0 && g != g_req) continue;
     for (int qbuf = 2; qbuf >= 1; --qbuf) {
-      int stages = (budget - fixed - qbuf * g * (int)p.q_tile_bytes) / kv_stage;
+      // one pair row per item: the two softmax warpgroups take two neighbouring query tiles
+      const bool split = g == 1 && allow_q_split && p.n_qt >= 2;
+      const int streams = split ? 2 : g;
+      int stages = (budget - fixed - qbuf * streams * (int)p.q_tile_bytes) / kv_stage;
       if (stages > kMaxKvStages) stages = kMaxKvStages;
       if (stages < 2) continue;
       const long long groups = (p.B1 + g - 1) / g;
-      const long long items = groups * p.B2 * p.n_qt;
+      const long long items = groups * p.B2 * (split ? (p.n_qt + 1) / 2 : p.n_qt);
       const long long rounds = (items + dev.sm_count - 1) / dev.sm_count;
       // streams alternate between the two softmax warpgroups: an odd count leaves one idle slot.
       // A CTA's time, in logits-tile times of one warpgroup: per item n_kt tiles for each of its
       // slots / 2 streams plus about 0.8 for the epilogue and the hand-over to the next item; with
       // a single Q buffer the next item's Q tiles are loaded and scaled at the hand-over (about 0.5:
       // each stream's tile is replaced as soon as its last Q K^T has finished).
-      const int slots = (g & 1) ? g + 1 : g;
+      const int slots = split ? 2 : ((g & 1) ? g + 1 : g);
       double cost = (double)rounds * (p.n_kt * (slots / 2) + 0.8 + (qbuf == 1 ? 0.5 : 0.0));
       // a K/V tile takes about two thousand cycles to arrive, most of a logits tile's time: with a
       // short ring the MMAs wait for their operands (measured: 4 stages cost about 3 %)
       static const double kRingPenalty[7] = {0, 0, 1.4, 1.15, 1.03, 1.0, 1.0};
       cost *= kRingPenalty[stages];
+      if (split) cost *= 1.02;   // query-tile streams share no bias tile: pair rows win a tie
       if (best_g == 0 || cost < best_cost) { best_g = g; best_cost = cost; best_stages = stages; best_qbuf = qbuf; }
     }
   }
   if (best_g == 0) return AF3K_ERR_BAD_SHAPE;
   p.G = best_g;
+  p.q_split = (best_g == 1 && allow_q_split && p.n_qt >= 2) ? 1 : 0;
+  p.n_streams = p.q_split ? 2 : p.G;
   p.kv_stages = best_stages;
   p.q_buffers = best_qbuf;
   const long long groups = (p.B1 + p.G - 1) / p.G;
-  const long long items = groups * p.B2 * p.n_qt;
+  const long long items = groups * p.B2 * (p.q_split ? (p.n_qt + 1) / 2 : p.n_qt);
   if (items > 0x7fffffff) return AF3K_ERR_BAD_SHAPE;
   p.n_items = (int)items;
 
   uint32_t off = 0;
-  p.off_q = off;      off += p.q_buffers * p.G * p.q_tile_bytes;
+  p.off_q = off;      off += p.q_buffers * p.n_streams * p.q_tile_bytes;
   p.off_kv = off;     off += p.kv_stages * kv_stage;
   p.off_bias = off;   off += kBiasStages * kBiasTileBytes;
   p.off_bar = off;    off += kBarrierBlockBytes;
@@ -421,8 +445,13 @@ int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, c
   if (rc != AF3K_OK) return rc;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
 
+  // fp8 q/k run the tensor-core-bias kernel when the bias is (or can be) staged pre-divided by
+  // the logit scale; bf16 q/k always do
+  const bool fp8_with_tc_bias = fp8 && (d.bias_prescaled ||
+      (workspace != nullptr && aligned16(workspace) &&
+       workspace_bytes >= (size_t)d.B2 * d.Sq * staged_bias_pitch(d.Sk) * 2));
   Plan plan;
-  rc = make_plan(d, *dev, &plan);
+  rc = make_plan(d, *dev, &plan, !fp8 || fp8_with_tc_bias);
   if (rc != AF3K_OK) return rc;
   AttnParams& p = plan.p;
   if (plan.smem_bytes > (size_t)(dev->max_smem_optin - kStaticSmemReserve)) return AF3K_ERR_BAD_SHAPE;
@@ -481,8 +510,16 @@ int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, c
     attention_kernel<true, true><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
   else if (dbg)
     attention_kernel<true, false><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
-  else if (tc_bias)
-    attention_kernel<false, true><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
+  else if (tc_bias) {
+    switch (exp_mode()) {
+      case 2: attention_kernel<false, true, 2><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b); break;
+      case 3: attention_kernel<false, true, 3><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b); break;
+      case 4: attention_kernel<false, true, 4><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b); break;
+      case 5: attention_kernel<false, true, 5><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b); break;
+      case 8: attention_kernel<false, true, 8><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b); break;
+      default: attention_kernel<false, true><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
+    }
+  }
   else
     attention_kernel<false, false><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
   cudaError_t e = cudaGetLastError();
@@ -517,7 +554,7 @@ int af3k_describe_plan(const af3k_attention_desc* desc, int32_t* out6) {
   out6[2] = plan.p.n_items;
   out6[3] = plan.grid;
   out6[4] = (int32_t)plan.smem_bytes;
-  out6[5] = (int32_t)kOCol + plan.p.G * plan.p.nv;
+  out6[5] = (int32_t)kOCol + plan.p.n_streams * plan.p.nv;
   return AF3K_OK;
 }
 

@@ -74,6 +74,19 @@ constexpr uint32_t kBarrierBlockBytes = 512;
 constexpr uint32_t kIdentBytes = 512;        // 16 x 16 bf16 identity, K-major core matrices
 constexpr float kLog2e = 1.4426950408889634f;
 
+// How the softmax threads evaluate the exponentials of a logits tile (template parameter kExp):
+//   0        every value with ex2.approx.f32 on the XU (16 lanes per SM and clock)
+//   1 .. 7   that many of every eight column pairs with a degree-3 polynomial on the FMA pipe
+//            (round-to-nearest split y = j + f, 2^f by Horner, j added into the exponent field),
+//            the rest on the XU, so that both pipes work on the same tile
+//   8        packed half precision: the exponent arguments of two keys are rounded to f16 and one
+//            ex2.approx.f16x2 gives both weights, already in the 16-bit form the second GEMM reads
+//            (P is then f16, not bf16; V stays bf16)
+constexpr int kExpF32 = 0, kExpF16x2 = 8;
+constexpr float kPolyC0 = 0.9999280571937561f, kPolyC1 = 0.6932609677314758f, kPolyC2 = 0.2426111251115799f,
+                kPolyC3 = 0.0551716685295105f;   // 2^f on [-0.5, 0.5], relative error 7.5e-5
+constexpr float kPolyMagic = 12582912.0f;        // 1.5 * 2^23: y + magic has round(y) in its low mantissa bits
+
 enum StatusBits : int {
   kStatusOk = 0,
   kStatusWaitTimeout = 1,   // a bounded mbarrier wait ran out
@@ -82,7 +95,9 @@ enum StatusBits : int {
 struct AttnParams {
   int B1, B2, Sq, Sk, D;
   int n_qt, n_kt;
-  int G;                 // streams (pair rows) per work item
+  int G;                 // pair rows per work item
+  int q_split;           // 1: the streams of an item are two neighbouring query tiles of ONE pair row (G == 1)
+  int n_streams;         // streams per work item: G, or 2 with q_split
   int n_items;
   int qk_row_bytes;      // smem bytes per Q / K tile row: 32, 64 or 128 (= swizzle span)
   int v_row_bytes;       // same for V
@@ -192,19 +207,27 @@ __device__ __forceinline__ uint32_t swizzle_layout_code(int row_bytes) {
   return row_bytes == 128 ? 2u : (row_bytes == 64 ? 4u : 6u);
 }
 
+// A work item: head h, first query tile qt, first pair row r0, gv streams.  Normally the streams
+// are gv pair rows sharing one query tile index (and therefore one bias tile per key tile).  With
+// q_split (chosen when there is a single pair row per item, so that the second softmax warpgroup
+// is not left idle) they are gv neighbouring query tiles of pair row r0, each with its own bias
+// tiles.
 struct Item {
   int qt, h, r0, gv;
 };
 __device__ __forceinline__ Item decode_item(const AttnParams& p, int item) {
   Item it;
-  it.qt = item % p.n_qt;
-  int t = item / p.n_qt;
+  const int nq = p.q_split ? (p.n_qt + 1) >> 1 : p.n_qt;
+  it.qt = (item % nq) << p.q_split;
+  int t = item / nq;
   it.h = t % p.B2;
   int rg = t / p.B2;
   it.r0 = rg * p.G;
-  it.gv = min(p.G, p.B1 - it.r0);
+  it.gv = p.q_split ? min(2, p.n_qt - it.qt) : min(p.G, p.B1 - it.r0);
   return it;
 }
+__device__ __forceinline__ int stream_row(const AttnParams& p, const Item& it, int s) { return p.q_split ? it.r0 : it.r0 + s; }
+__device__ __forceinline__ int stream_qt(const AttnParams& p, const Item& it, int s) { return p.q_split ? it.qt + s : it.qt; }
 
 // Q buffer of the CTA's j-th item and how often that buffer was used before.
 __device__ __forceinline__ uint32_t q_buf(const AttnParams& p, uint32_t j) { return p.q_buffers == 2 ? (j & 1u) : 0u; }
@@ -226,8 +249,8 @@ __device__ void producer_role(const Ctx& c, const CUtensorMap* tm_q, const CUten
       // the buffer's previous user must have finished its last Q K^T of this stream
       if (use >= 1) AF3K_WAIT_NORET(c, BarIdx::q_empty + slot, (use - 1) & 1);
       mbar_arrive_expect_tx(bar_addr(c, BarIdx::q_full + slot), p.q_tile_bytes);
-      tma_load_4d(c.smem + p.off_q + (buf * p.G + s) * p.q_tile_bytes, tm_q, bar_addr(c, BarIdx::q_full + slot),
-                  0, it.qt * kTile, it.h, it.r0 + s);
+      tma_load_4d(c.smem + p.off_q + (buf * p.n_streams + s) * p.q_tile_bytes, tm_q, bar_addr(c, BarIdx::q_full + slot),
+                  0, stream_qt(p, it, s) * kTile, it.h, stream_row(p, it, s));
     }
     return true;
   };
@@ -237,23 +260,25 @@ __device__ void producer_role(const Ctx& c, const CUtensorMap* tm_q, const CUten
   for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++icount) {
     const Item it = decode_item(p, item);
     for (int kt = 0; kt < p.n_kt; ++kt) {
-      const uint32_t bst = bcount % kBiasStages;
-      if (bcount >= kBiasStages)
-        AF3K_WAIT(c, BarIdx::bias_empty + bst, ((bcount / kBiasStages) - 1) & 1);
-      const uint32_t bfull = bar_addr(c, BarIdx::bias_full + bst);
-      const uint32_t bdst = c.smem + p.off_bias + bst * kBiasTileBytes;
-      mbar_arrive_expect_tx(bfull, kBiasTileBytes);
-      tma_load_3d(bdst, tm_bias, bfull, kt * kTile, it.qt * kTile, it.h);
-      tma_load_3d(bdst + kBiasTileBytes / 2, tm_bias, bfull, kt * kTile + 64, it.qt * kTile, it.h);
-      ++bcount;
       for (int s = 0; s < it.gv; ++s) {
+        if (s == 0 || p.q_split) {   // one bias tile per key tile, or per stream when the streams are query tiles
+          const uint32_t bst = bcount % kBiasStages;
+          if (bcount >= kBiasStages)
+            AF3K_WAIT(c, BarIdx::bias_empty + bst, ((bcount / kBiasStages) - 1) & 1);
+          const uint32_t bfull = bar_addr(c, BarIdx::bias_full + bst);
+          const uint32_t bdst = c.smem + p.off_bias + bst * kBiasTileBytes;
+          mbar_arrive_expect_tx(bfull, kBiasTileBytes);
+          tma_load_3d(bdst, tm_bias, bfull, kt * kTile, stream_qt(p, it, s) * kTile, it.h);
+          tma_load_3d(bdst + kBiasTileBytes / 2, tm_bias, bfull, kt * kTile + 64, stream_qt(p, it, s) * kTile, it.h);
+          ++bcount;
+        }
         const uint32_t st = ucount % nkv;
         if (ucount >= nkv) AF3K_WAIT(c, BarIdx::kv_empty + st, ((ucount / nkv) - 1) & 1);
         const uint32_t full = bar_addr(c, BarIdx::kv_full + st);
         const uint32_t kdst = c.smem + p.off_kv + st * (p.k_tile_bytes + p.v_tile_bytes);
         mbar_arrive_expect_tx(full, p.k_tile_bytes + p.v_tile_bytes);
-        tma_load_4d(kdst, tm_k, full, 0, kt * kTile, it.h, it.r0 + s);
-        tma_load_4d(kdst + p.k_tile_bytes, tm_v, full, 0, kt * kTile, it.h, it.r0 + s);
+        tma_load_4d(kdst, tm_k, full, 0, kt * kTile, it.h, stream_row(p, it, s));
+        tma_load_4d(kdst + p.k_tile_bytes, tm_v, full, 0, kt * kTile, it.h, stream_row(p, it, s));
         ++ucount;
       }
       if (kt == (p.q_buffers == 2 ? 0 : p.n_kt - 1) && item + (int)gridDim.x < p.n_items) {
@@ -285,7 +310,7 @@ __device__ __forceinline__ void scale_q_chunk(uint32_t addr, float scale, int la
 // The 128 mask-column values (bf16) of one logits tile, four per lane.
 __device__ __forceinline__ void mask_values(const AttnParams& p, const Item& it, int kt, int s, int lane,
                                             uint16_t masked, uint16_t (&val)[4]) {
-  const uint8_t* mrow = p.mask != nullptr ? p.mask + (long long)(it.r0 + s) * p.mask_row_stride : nullptr;
+  const uint8_t* mrow = p.mask != nullptr ? p.mask + (long long)stream_row(p, it, s) * p.mask_row_stride : nullptr;
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     const int key = kt * kTile + 32 * g + lane;
@@ -330,7 +355,7 @@ struct QScaler {
         }
       }
     }
-    scale_q_chunk(c.smem + p.off_q + (buf * p.G + tile) * p.q_tile_bytes + (chunk << 10), p.scale, lane);
+    scale_q_chunk(c.smem + p.off_q + (buf * p.n_streams + tile) * p.q_tile_bytes + (chunk << 10), p.scale, lane);
     if (++chunk == (p.q_tile_bytes >> 10)) {
       fence_proxy_async_smem();    // make the generic-proxy stores visible to the tensor core
       __syncwarp();
@@ -447,8 +472,8 @@ __device__ void qk_issuer_role(const Ctx& c) {
     const Item it = decode_item(p, item);
     const int gv = it.gv;
     for (int kt = 0; kt < p.n_kt; ++kt) {
-      if (kTcBias) AF3K_WAIT_WARP(c, BarIdx::bias_full + bst, b_par);
       for (int s = 0; s < gv; ++s) {
+        if (kTcBias && (s == 0 || p.q_split)) AF3K_WAIT_WARP(c, BarIdx::bias_full + bst, b_par);
         const int b = s & 1;
         // the softmax warpgroup of this buffer must have read the previous logits tile
         if (b) {
@@ -462,7 +487,7 @@ __device__ void qk_issuer_role(const Ctx& c) {
         if (kt == 0) AF3K_WAIT_WARP(c, (p.scale_q ? BarIdx::q_scaled : BarIdx::q_full) + qslot, q_use(p, icount) & 1);
         AF3K_WAIT_WARP(c, BarIdx::kv_full + st, kv_par);
         tc_fence_after();
-        const uint32_t a_lo = qd_lo + (q_buf(p, icount) * p.G + s) * q_step;
+        const uint32_t a_lo = qd_lo + (q_buf(p, icount) * p.n_streams + s) * q_step;
         const uint32_t b_lo = kd_lo + st * stage_step;
         const uint32_t s_tmem = c.tmem + kSCol + b * kTile;
         const uint32_t slot16 = st * (kMaskPanelBytes >> 4);
@@ -492,12 +517,12 @@ __device__ void qk_issuer_role(const Ctx& c) {
         }
         __syncwarp();
         if (++st == nkv) { st = 0; kv_par ^= 1; }
-      }
-      if (kTcBias) {
-        // every stream's bias MMAs of this key tile are issued: the bias stage is free when they finish
-        if (leader) tc_commit(bar_addr(c, BarIdx::bias_empty + bst));
-        __syncwarp();
-        if (++bst == kBiasStages) { bst = 0; b_par ^= 1; }
+        if (kTcBias && (s == gv - 1 || p.q_split)) {
+          // every bias MMA that reads this stage is issued: the stage is free when they finish
+          if (leader) tc_commit(bar_addr(c, BarIdx::bias_empty + bst));
+          __syncwarp();
+          if (++bst == kBiasStages) { bst = 0; b_par ^= 1; }
+        }
       }
     }
   }
@@ -506,7 +531,7 @@ __device__ void qk_issuer_role(const Ctx& c) {
 // O += P V for every tile, in order.  This warp mostly waits for the softmax warpgroups, so (bf16
 // q/k) it also scales the Q tiles: the first item's up front, the next item's in 1 KB pieces
 // while it waits, what is left when the item's last P V has been issued.
-template <bool kTcBias>
+template <bool kTcBias, int kExp>
 __device__ void pv_issuer_role(const Ctx& c, int lane) {
   const AttnParams& p = *c.p;
   const bool leader = elect_one();
@@ -518,7 +543,7 @@ __device__ void pv_issuer_role(const Ctx& c, int lane) {
   }
   const uint32_t nkv = p.kv_stages;
   const uint32_t v_layout = swizzle_layout_code(p.v_row_bytes);
-  const uint32_t idesc_pv = make_idesc(1u, 1u, 0u, 1u, (uint32_t)p.nv);
+  const uint32_t idesc_pv = make_idesc(kExp == kExpF16x2 ? 0u : 1u, 1u, 0u, 1u, (uint32_t)p.nv);   // A = P (f16 or bf16), B = V (bf16)
   const uint32_t kv_stage_bytes = p.k_tile_bytes + p.v_tile_bytes;
   const uint64_t vd0 = make_smem_desc(c.smem + p.off_kv + p.k_tile_bytes, p.v_tile_bytes,
                                       8 * p.v_row_bytes, v_layout);
@@ -617,7 +642,7 @@ __device__ __forceinline__ void max_half(const uint32_t (&xr)[kTile], float& mxa
 // One 128 x 128 logits tile of one stream; the thread owns row `row` (TMEM lane).
 // m_run is the reference maximum the running sums are scaled by (it may lag the true maximum by
 // up to kLazyRescaleLog2 bits), l_run the running sum of the fp32 weights.
-template <bool kTcBias>
+template <bool kTcBias, int kExp>
 __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, int lane,
                                              uint32_t s_taddr, uint32_t p_taddr, uint32_t o_taddr,
                                              int nv, uint32_t bias_row, uint32_t row7, float scale,
@@ -681,6 +706,11 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
   const float nml = -m_use * ef;
   const uint64_t nml2 = pack_f32x2(nml, nml);
   uint64_t suma = pack_f32x2(0.f, 0.f), sumb = suma;
+  const uint64_t magic2 = pack_f32x2(kPolyMagic, kPolyMagic), nmagic2 = pack_f32x2(-kPolyMagic, -kPolyMagic);
+  const uint64_t mone2 = pack_f32x2(-1.f, -1.f);
+  const uint64_t pc0 = pack_f32x2(kPolyC0, kPolyC0), pc1 = pack_f32x2(kPolyC1, kPolyC1),
+                 pc2 = pack_f32x2(kPolyC2, kPolyC2), pc3 = pack_f32x2(kPolyC3, kPolyC3);
+  uint32_t hacc = 0;
   // The first kHeld column groups are computed before anything is written: the P buffer and the
   // O accumulator only become free when the previous P V of this warpgroup has finished, and that
   // wait is taken as late as the registers allow.
@@ -693,13 +723,43 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
       const int col = cidx * 16 + 2 * i;
       float y0, y1;
       const uint64_t x2 = pack_f32x2(__uint_as_float(xr[col]), __uint_as_float(xr[col + 1]));
-      if (kTcBias) unpack_f32x2(fma_f32x2(x2, l2e2, nml2), y0, y1);
-      else         unpack_f32x2(mul_f32x2(add_f32x2(x2, nm2), l2e2), y0, y1);
-      const float p0 = ex2_approx(y0);
-      const float p1 = ex2_approx(y1);
-      if (i & 1) sumb = add_f32x2(sumb, pack_f32x2(p0, p1));
-      else       suma = add_f32x2(suma, pack_f32x2(p0, p1));
-      pk[cidx][i] = pack_bf16x2(p0, p1);
+      const uint64_t y2 = kTcBias ? fma_f32x2(x2, l2e2, nml2) : mul_f32x2(add_f32x2(x2, nm2), l2e2);
+      unpack_f32x2(y2, y0, y1);
+      if (kExp == kExpF16x2) {
+        // two weights per XU instruction; their sum is taken from the rounded values, four words
+        // (eight keys) in f16, then widened
+        const uint32_t w = ex2_f16x2(pack_f16x2(y0, y1));
+        pk[cidx][i] = w;
+        if ((i & 3) == 0) hacc = w; else hacc = add_f16x2(hacc, w);
+        if ((i & 3) == 3) {
+          const uint64_t wide = f16x2_to_f32x2(hacc);
+          if (i & 4) sumb = add_f32x2(sumb, wide); else suma = add_f32x2(suma, wide);
+        }
+      } else if (kExp >= 1 && kExp <= 7 && i < kExp) {
+        // polynomial share.  y is at most kLazyRescaleLog2; below -126 the weight is zero (also for
+        // the -2^47 / -inf of masked and absent keys), which the clamp and the exponent add give:
+        // j = -126 and f = 0 leave 2^-126 * c0, and bf16 rounding of P drops nothing that matters
+        const uint64_t yc2 = pack_f32x2(fmaxf(y0, -126.0f), fmaxf(y1, -126.0f));
+        const uint64_t t2 = add_f32x2(yc2, magic2);              // magic + round(y)
+        const uint64_t f2 = fma_f32x2(add_f32x2(t2, nmagic2), mone2, yc2);   // y - round(y) in [-0.5, 0.5]
+        uint64_t q2 = fma_f32x2(pc3, f2, pc2);
+        q2 = fma_f32x2(q2, f2, pc1);
+        q2 = fma_f32x2(q2, f2, pc0);
+        float t0, t1, q0, q1;
+        unpack_f32x2(t2, t0, t1);
+        unpack_f32x2(q2, q0, q1);
+        const float p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+        const float p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+        if (i & 1) sumb = add_f32x2(sumb, pack_f32x2(p0, p1));
+        else       suma = add_f32x2(suma, pack_f32x2(p0, p1));
+        pk[cidx][i] = pack_bf16x2(p0, p1);
+      } else {
+        const float p0 = ex2_approx(y0);
+        const float p1 = ex2_approx(y1);
+        if (i & 1) sumb = add_f32x2(sumb, pack_f32x2(p0, p1));
+        else       suma = add_f32x2(suma, pack_f32x2(p0, p1));
+        pk[cidx][i] = pack_bf16x2(p0, p1);
+      }
     }
     if (dbg != nullptr) {
 #pragma unroll
@@ -747,7 +807,7 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
   return true;
 }
 
-template <bool kDebug, bool kTcBias>
+template <bool kDebug, bool kTcBias, int kExp>
 __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
   const AttnParams& p = *c.p;
   const int row = wq * 32 + lane;                    // row of the 128-query tile == TMEM lane
@@ -796,7 +856,7 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
         float* dbg = nullptr;
         if (kDebug && p.debug != nullptr && blockIdx.x == 0 && icount == 0 && s == 0 && kt == 0)
           dbg = p.debug + (size_t)row * kTile;
-        if (!softmax_tile<kTcBias>(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row, row & 7, scale,
+        if (!softmax_tile<kTcBias, kExp>(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row, row & 7, scale,
                           kt == 0, ucnt > 0, BarIdx::kv_empty + (int)prev_stage, prev_round & 1, m_run,
                           l_run, ts))
           return;
@@ -831,11 +891,11 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
     if (wg < it.gv) AF3K_WAIT_WARP(c, BarIdx::kv_empty + (int)prev_stage, prev_round & 1);
     tc_fence_after();
     if (kDebug && last_ts != nullptr) last_ts[6] = clock64();
-    const int qrow = it.qt * kTile + row;
     for (int s = wg; s < it.gv; s += 2) {
+      const int qrow = stream_qt(p, it, s) * kTile + row;
       const float inv = __frcp_rn(s == wg ? l_st[0] : l_st[1]);
       const uint32_t o_taddr = c.tmem + lane_sel + kOCol + s * p.nv;
-      __nv_bfloat16* orow = p.out + (long long)(it.r0 + s) * p.out_stride_b1 +
+      __nv_bfloat16* orow = p.out + (long long)stream_row(p, it, s) * p.out_stride_b1 +
                             (long long)it.h * p.out_stride_b2 + (long long)qrow * p.out_stride_s;
       for (int c0 = 0; c0 < p.nv; c0 += 16) {
         uint32_t o[16];
@@ -871,7 +931,7 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
 }
 
 // ------------------------------------------------------------------ kernel
-template <bool kDebug, bool kTcBias>
+template <bool kDebug, bool kTcBias, int kExp = kExpF32>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -951,13 +1011,13 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
     } else if (warp == 1) {
       qk_issuer_role<kTcBias>(c);
     } else if (warp == 2) {
-      pv_issuer_role<kTcBias>(c, lane);
+      pv_issuer_role<kTcBias, kExp>(c, lane);
     } else if (warp == 3) {
       if (p.mask_col) mask_writer_role(c, lane);
     }
   } else {
     setmaxnreg_inc<kRegsSoftmax>();
-    softmax_role<kDebug, kTcBias>(c, (warp - 4) >> 2, warp & 3, lane);
+    softmax_role<kDebug, kTcBias, kExp>(c, (warp - 4) >> 2, warp & 3, lane);
   }
 
   tc_fence_before();

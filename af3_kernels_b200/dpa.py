@@ -329,6 +329,8 @@ def dot_product_attention_host(
     if not torch.cuda.is_available():
         raise RuntimeError("af3_kernels_b200 needs a CUDA device (there is no CPU fallback)")
     dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
     if q.dim() != 4:
         raise ValueError("q, k, v must be 4-D [B1, B2, S, D]")
     B1, B2, Sq, D = q.shape
@@ -344,7 +346,9 @@ def dot_product_attention_host(
 
     with torch.cuda.device(dev):
         main = torch.cuda.current_stream()
-        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        st = _host_path_state(dev, q, k, v, (B1, B2, Sq, D))
+        s_in, s_out = st["s_in"], st["s_out"]
+        dq, dk, dv, do = st["q"], st["k"], st["v"], st["o"]
         s_in.wait_stream(main)
         s_out.wait_stream(main)
         # bias and mask once; an fp32 bias is rounded to bf16 here instead of once per row block
@@ -358,10 +362,6 @@ def dot_product_attention_host(
             and B1 != 1
         if per_row_mask:
             mask_d = mask_d.reshape(B1, mask_d.shape[-1])
-        dq = torch.empty(q.shape, dtype=q.dtype, device=dev)
-        dk = torch.empty(k.shape, dtype=k.dtype, device=dev)
-        dv = torch.empty(v.shape, dtype=v.dtype, device=dev)
-        do = torch.empty((B1, B2, Sq, D), dtype=torch.bfloat16, device=dev)
         for i in range(n_chunks):
             lo, hi = bounds[i], bounds[i + 1]
             if lo == hi:
@@ -382,8 +382,34 @@ def dot_product_attention_host(
                 s_out.wait_event(done)
                 out[lo:hi].copy_(do[lo:hi], non_blocking=True)
         main.wait_stream(s_out)
-        for t in (dq, dk, dv, do):
-            t.record_stream(s_in)
-            t.record_stream(s_out)
         s_out.synchronize()
+        # the call synchronised anyway: the device status word costs nothing to read here
+        status = read_status(dev)
+        if status[0] != 0:
+            raise RuntimeError(
+                f"af3k kernel reported status {status[0]} (wait timeout: barrier slot {status[1] - 1}, "
+                f"block {status[2]}, warp {status[3]}); the output is not valid")
     return out
+
+
+# Copy streams and device staging buffers of the host-tensor path, kept between calls (per device
+# and problem shape) so that a caller in a loop does not create streams and allocate 4 buffers
+# per call.  Calls on one device are serialised by the synchronisation at the end of each call.
+_host_state: dict = {}
+
+
+def _host_path_state(dev, q, k, v, out_shape):
+    key = (dev.index, tuple(q.shape), q.dtype, tuple(k.shape), k.dtype, tuple(v.shape), v.dtype)
+    st = _host_state.get(key)
+    if st is None:
+        if len(_host_state) >= 2:          # keep at most two shapes' worth of buffers alive
+            _host_state.pop(next(iter(_host_state)))
+        st = {
+            "s_in": torch.cuda.Stream(device=dev), "s_out": torch.cuda.Stream(device=dev),
+            "q": torch.empty(q.shape, dtype=q.dtype, device=dev),
+            "k": torch.empty(k.shape, dtype=k.dtype, device=dev),
+            "v": torch.empty(v.shape, dtype=v.dtype, device=dev),
+            "o": torch.empty(out_shape, dtype=torch.bfloat16, device=dev),
+        }
+        _host_state[key] = st
+    return st

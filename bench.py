@@ -104,6 +104,26 @@ class ClockSampler:
         }
 
 
+def bind_to_gpu_cpus(index: int):
+    """Restricts this process to the host CPUs NVML reports as local to GPU ``index`` (a read-only
+    query; the affinity is a setting of this process, not of the GPU), so that with several ranks
+    each one's pinned buffers and copy threads sit on its GPU's NUMA node.  Returns the CPU count
+    it ended up with, or None when nothing was changed."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        local = {i * 64 + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        target = local & os.sched_getaffinity(0)
+        if target:
+            os.sched_setaffinity(0, target)
+            return len(target)
+    except Exception:
+        pass
+    return None
+
+
 # --------------------------------------------------------------------------- CPU arm
 def _cpu_inputs(O, name, rows):
     c = O.CONFIGS[name]
@@ -406,6 +426,7 @@ def main():
         raise SystemExit("bench.py --impl ours needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    bound_cpus = bind_to_gpu_cpus(local_rank) if world > 1 else None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
@@ -505,9 +526,39 @@ def main():
     if world > 1:
         dist.all_reduce(e2e_total, op=dist.ReduceOp.MAX)
     e2e_ms = e2e_total.item() / e2e_steps
-    e2e = {"value": world * flops_call / (e2e_ms / 1e3) / 1e12, "unit": UNIT,
+    # the host link by itself: q host -> device, result device -> host, then both at once
+    dq = torch.empty_like(q)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def link_gbs(h2d_on, d2h_on, reps=3):
+        sync_all()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        s1.wait_event(a)
+        s2.wait_event(a)
+        for _ in range(reps):
+            if h2d_on:
+                with torch.cuda.stream(s1):
+                    dq.copy_(host["q"], non_blocking=True)
+            if d2h_on:
+                with torch.cuda.stream(s2):
+                    out_host.copy_(dq if not h2d_on else v, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(s1)
+        torch.cuda.current_stream().wait_stream(s2)
+        b.record()
+        torch.cuda.synchronize()
+        nbytes = reps * dq.numel() * dq.element_size() * (int(h2d_on) + int(d2h_on))
+        return nbytes / (a.elapsed_time(b) / 1e3) / 1e9
+
+    link = None
+    if q.dtype == torch.bfloat16:
+        link = {"h2d_alone_gbs": link_gbs(True, False), "d2h_alone_gbs": link_gbs(False, True),
+                "both_directions_total_gbs": link_gbs(True, True),
+                "what": "pinned host memory <-> this GPU, 151 MB copies; with N > 1 every rank copies at once"}
+    del dq
+    e2e = {"value": world * flops_call / (e2e_ms / 1e3) / 1e12, "unit": UNIT, "host_link": link,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-           "steps": e2e_steps, "calls_per_step": 1,
+           "steps": e2e_steps, "calls_per_step": 1, "cpus_bound_to_gpu_node": bound_cpus,
            "what": "dot_product_attention_cpp on pinned host tensors: H2D of q/k/v/bias/mask, kernel, "
                    "D2H of the result inside the timed region, every step"}
     del host, out_host
