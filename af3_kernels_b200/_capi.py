@@ -34,6 +34,7 @@ EXPORTED_SYMBOLS = (
     "af3k_selftest_wait_timeout",
     "af3k_pair_bias",
     "af3k_sigmoid_gate",
+    "af3k_qkvg_projection",
 )
 
 
@@ -112,6 +113,8 @@ def load() -> ctypes.CDLL:
     lib.af3k_pair_bias.restype = ctypes.c_int
     lib.af3k_pair_bias.argtypes = [vp, ctypes.c_int32, i64, i64, i64, i64, vp, vp, vp, ctypes.c_float, vp, vp,
                                    i64, vp]
+    lib.af3k_qkvg_projection.restype = ctypes.c_int
+    lib.af3k_qkvg_projection.argtypes = [vp, vp, i64, i64, i64, ctypes.c_float, vp, vp, vp, vp, vp, vp]
     lib.af3k_sigmoid_gate.restype = ctypes.c_int
     lib.af3k_sigmoid_gate.argtypes = [vp, vp, vp, i64, vp]
     _lib = lib

@@ -55,5 +55,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+PROBE_SRC = os.path.join(CSRC, "xu_pipe_probe.cu")
+PROBE_PATH = os.path.join(_HERE, "xu_pipe_probe")
+
+
+def build_probe() -> str:
+    """Compiles the stand-alone instruction-pipe probe (csrc/xu_pipe_probe.cu): the measurements
+    behind the softmax loop's formulation.  Not part of the library."""
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", PROBE_PATH, PROBE_SRC]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("nvcc failed building xu_pipe_probe")
+    return PROBE_PATH
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--probe" in sys.argv:
+        print(build_probe())
+    else:
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

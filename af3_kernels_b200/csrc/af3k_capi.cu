@@ -13,6 +13,7 @@
 
 #include "attn_sm100.cuh"
 #include "pair_bias_sm100.cuh"
+#include "proj_sm100.cuh"
 
 namespace {
 
@@ -43,17 +44,6 @@ long long wait_limit_cycles() {
   if (v <= 0) v = 2000000000LL;
   g_wait_limit.store(v);
   return v;
-}
-
-// Experiment switch: which exponential formulation the tensor-core-bias kernel uses (see kExp in
-// attn_sm100.cuh).  Read once from AF3K_EXP_MODE.
-int exp_mode() {
-  static int mode = -1;
-  if (mode < 0) {
-    const char* e = std::getenv("AF3K_EXP_MODE");
-    mode = e ? std::atoi(e) : 0;
-  }
-  return mode;
 }
 
 PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
@@ -99,20 +89,21 @@ int device_info(DeviceInfo** out) {
     // the opt-in limit covers static + dynamic shared memory; the kernel has a few static bytes
     const int dyn = d.max_smem_optin - kStaticSmemReserve;
     const cudaFuncAttribute attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
-    if ((e = cudaFuncSetAttribute(attention_kernel<false, false>, attr, dyn)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(attention_kernel<false, true>, attr, dyn)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(attention_kernel<true, false>, attr, dyn)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(attention_kernel<true, true>, attr, dyn)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(attention_kernel<false, true, 2>, attr, dyn)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(attention_kernel<false, true, 3>, attr, dyn)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(attention_kernel<false, true, 4>, attr, dyn)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(attention_kernel<false, true, 5>, attr, dyn)) != cudaSuccess ||
-        (e = cudaFuncSetAttribute(attention_kernel<false, true, 8>, attr, dyn)) != cudaSuccess)
+    const void* kernels[] = {
+        (const void*)attention_kernel<false, false>, (const void*)attention_kernel<true, false>,
+        (const void*)attention_kernel<false, true>,  (const void*)attention_kernel<true, true>,
+    };
+    e = cudaSuccess;
+    for (const void* kfn : kernels)
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(kfn, attr, dyn);
+    if (e != cudaSuccess)
       return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize)", e);
     if ((e = cudaFuncSetAttribute(pair_bias_kernel_t<float>, attr, PbTile<float>::kSmemBytes)) != cudaSuccess ||
         (e = cudaFuncSetAttribute(pair_bias_kernel_t<__nv_bfloat16>, attr, PbTile<__nv_bfloat16>::kSmemBytes)) !=
             cudaSuccess)
       return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize, pair_bias)", e);
+    if ((e = cudaFuncSetAttribute(qkvg_projection_kernel, attr, (int)kProjSmemBytes)) != cudaSuccess)
+      return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize, qkvg_projection)", e);
     d.attr_set = true;
   }
   *out = &d;
@@ -504,24 +495,15 @@ int af3k_dot_product_attention(const af3k_attention_desc* desc, const void* q, c
   // scale, bias and mask all come out of the tensor core, except for fp8 q/k without a staging
   // copy of the bias: there the softmax threads apply scale and bias in fp32
   const bool tc_bias = !fp8 || fp8_tc;
-  p.scale_q = fp8 ? 0 : 1;
+  p.scale_q = (fp8 || d.softmax_scale == 1.0f) ? 0 : 1;   // a scale of exactly 1 (q already scaled by its producer) needs no pass over Q
   const bool dbg = p.debug != nullptr;
-  if (dbg && tc_bias)
-    attention_kernel<true, true><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
-  else if (dbg)
-    attention_kernel<true, false><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
-  else if (tc_bias) {
-    switch (exp_mode()) {
-      case 2: attention_kernel<false, true, 2><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b); break;
-      case 3: attention_kernel<false, true, 3><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b); break;
-      case 4: attention_kernel<false, true, 4><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b); break;
-      case 5: attention_kernel<false, true, 5><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b); break;
-      case 8: attention_kernel<false, true, 8><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b); break;
-      default: attention_kernel<false, true><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
-    }
+#define AF3K_LAUNCH(...) attention_kernel<__VA_ARGS__><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b)
+  if (!tc_bias) {
+    if (dbg) AF3K_LAUNCH(true, false); else AF3K_LAUNCH(false, false);
+  } else {
+    if (dbg) AF3K_LAUNCH(true, true); else AF3K_LAUNCH(false, true);
   }
-  else
-    attention_kernel<false, false><<<plan.grid, kThreads, plan.smem_bytes, stream>>>(p, tm_q, tm_k, tm_v, tm_b);
+#undef AF3K_LAUNCH
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("launch attention_kernel", e);
   ++launches;
@@ -631,6 +613,54 @@ int af3k_pair_bias(const void* pair, int32_t pair_dtype, int64_t R, int64_t N, i
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("launch pair_bias_kernel", e);
+  t_last_launches = 1;
+  return AF3K_OK;
+}
+
+int af3k_qkvg_projection(const void* x, const void* w4, int64_t R, int64_t N, int64_t H, float q_scale,
+                         void* q, void* k, void* v, void* gate, int* status_dev, void* stream_v) {
+  t_last_launches = 0;
+  if (R < 0 || N < 0 || H < 1 || kProjC % H != 0 || (kProjC / H) % 8 != 0) return AF3K_ERR_BAD_SHAPE;
+  if (R > 0x7fffffff || N > 0x7fffffff || R * N > 0x7fffff00LL * 128) return AF3K_ERR_BAD_SHAPE;
+  if (R == 0 || N == 0) return AF3K_OK;
+  if (!x || !w4 || !q || !k || !v || !gate) return AF3K_ERR_NULL_POINTER;
+  if (!aligned16(x) || !aligned16(w4) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(gate))
+    return AF3K_ERR_BAD_ALIGNMENT;
+  DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev);
+  if (rc != AF3K_OK) return rc;
+  auto enc = tensor_map_encoder();
+  if (!enc) return driver_fail("cuTensorMapEncodeTiled entry point", -1);
+  const long long M = R * N;
+  if (M > 0x7fffffffLL) return AF3K_ERR_BAD_SHAPE;    // TMA coordinates are 32-bit
+  CUtensorMap tm_x, tm_w;
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)kProjC, (cuuint64_t)M};
+    cuuint64_t strides[1] = {(cuuint64_t)kProjC * 2};
+    cuuint32_t box[2] = {64, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return driver_fail("cuTensorMapEncodeTiled(x)", (int)r);
+    cuuint64_t wdims[2] = {(cuuint64_t)kProjC, (cuuint64_t)kProjOut};
+    cuuint32_t wbox[2] = {64, 256};
+    r = enc(&tm_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w4), wdims, strides, wbox, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return driver_fail("cuTensorMapEncodeTiled(w4)", (int)r);
+  }
+  ProjParams p;
+  p.M = M; p.N = (int)N; p.H = (int)H; p.D = kProjC / (int)H; p.q_scale = q_scale;
+  p.q = static_cast<__nv_bfloat16*>(q); p.k = static_cast<__nv_bfloat16*>(k);
+  p.v = static_cast<__nv_bfloat16*>(v); p.g = static_cast<__nv_bfloat16*>(gate);
+  p.status = status_dev;
+  p.wait_limit = wait_limit_cycles();
+  const long long n_tiles = (M + 127) / 128;
+  const unsigned grid = (unsigned)(n_tiles < dev->sm_count ? n_tiles : dev->sm_count);
+  qkvg_projection_kernel<<<grid, kProjThreads, kProjSmemBytes, reinterpret_cast<cudaStream_t>(stream_v)>>>(p, tm_x, tm_w);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail("launch qkvg_projection_kernel", e);
   t_last_launches = 1;
   return AF3K_OK;
 }

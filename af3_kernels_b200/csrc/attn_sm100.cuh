@@ -74,18 +74,10 @@ constexpr uint32_t kBarrierBlockBytes = 512;
 constexpr uint32_t kIdentBytes = 512;        // 16 x 16 bf16 identity, K-major core matrices
 constexpr float kLog2e = 1.4426950408889634f;
 
-// How the softmax threads evaluate the exponentials of a logits tile (template parameter kExp):
-//   0        every value with ex2.approx.f32 on the XU (16 lanes per SM and clock)
-//   1 .. 7   that many of every eight column pairs with a degree-3 polynomial on the FMA pipe
-//            (round-to-nearest split y = j + f, 2^f by Horner, j added into the exponent field),
-//            the rest on the XU, so that both pipes work on the same tile
-//   8        packed half precision: the exponent arguments of two keys are rounded to f16 and one
-//            ex2.approx.f16x2 gives both weights, already in the 16-bit form the second GEMM reads
-//            (P is then f16, not bf16; V stays bf16)
-constexpr int kExpF32 = 0, kExpF16x2 = 8;
-constexpr float kPolyC0 = 0.9999280571937561f, kPolyC1 = 0.6932609677314758f, kPolyC2 = 0.2426111251115799f,
-                kPolyC3 = 0.0551716685295105f;   // 2^f on [-0.5, 0.5], relative error 7.5e-5
-constexpr float kPolyMagic = 12582912.0f;        // 1.5 * 2^23: y + magic has round(y) in its low mantissa bits
+// Exponentials: every weight is one ex2.approx.f32 on the XU (16 lanes per SM and clock: 4 results per
+// clock and scheduler).  Measured alternatives that do not beat it here: ex2.approx.f16x2 / .bf16x2 take
+// 16 XU cycles per warp instruction (the same 4 results per clock), kind::f16 MMAs take no f16 A with a
+// bf16 B, and a degree-3 polynomial on the FMA pipe costs more issue slots than the ex2 it replaces.
 
 enum StatusBits : int {
   kStatusOk = 0,
@@ -531,7 +523,7 @@ __device__ void qk_issuer_role(const Ctx& c) {
 // O += P V for every tile, in order.  This warp mostly waits for the softmax warpgroups, so (bf16
 // q/k) it also scales the Q tiles: the first item's up front, the next item's in 1 KB pieces
 // while it waits, what is left when the item's last P V has been issued.
-template <bool kTcBias, int kExp>
+template <bool kTcBias>
 __device__ void pv_issuer_role(const Ctx& c, int lane) {
   const AttnParams& p = *c.p;
   const bool leader = elect_one();
@@ -543,7 +535,7 @@ __device__ void pv_issuer_role(const Ctx& c, int lane) {
   }
   const uint32_t nkv = p.kv_stages;
   const uint32_t v_layout = swizzle_layout_code(p.v_row_bytes);
-  const uint32_t idesc_pv = make_idesc(kExp == kExpF16x2 ? 0u : 1u, 1u, 0u, 1u, (uint32_t)p.nv);   // A = P (f16 or bf16), B = V (bf16)
+  const uint32_t idesc_pv = make_idesc(1u, 1u, 0u, 1u, (uint32_t)p.nv);   // A = P and B = V, both bf16 (kind::f16 takes no mixed pair)
   const uint32_t kv_stage_bytes = p.k_tile_bytes + p.v_tile_bytes;
   const uint64_t vd0 = make_smem_desc(c.smem + p.off_kv + p.k_tile_bytes, p.v_tile_bytes,
                                       8 * p.v_row_bytes, v_layout);
@@ -642,7 +634,7 @@ __device__ __forceinline__ void max_half(const uint32_t (&xr)[kTile], float& mxa
 // One 128 x 128 logits tile of one stream; the thread owns row `row` (TMEM lane).
 // m_run is the reference maximum the running sums are scaled by (it may lag the true maximum by
 // up to kLazyRescaleLog2 bits), l_run the running sum of the fp32 weights.
-template <bool kTcBias, int kExp>
+template <bool kTcBias>
 __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, int lane,
                                              uint32_t s_taddr, uint32_t p_taddr, uint32_t o_taddr,
                                              int nv, uint32_t bias_row, uint32_t row7, float scale,
@@ -650,33 +642,35 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
                                              uint32_t prev_pv_parity, float& m_run, float& l_run,
                                              long long* ts = nullptr) {
   uint32_t xr[kTile];
-  tmem_ld_x32(s_taddr + 0, &xr[0]);
-  tmem_ld_x32(s_taddr + 32, &xr[32]);
-  tc_wait_ld();
-  tmem_ld_x32(s_taddr + 64, &xr[64]);
-  tmem_ld_x32(s_taddr + 96, &xr[96]);
-  if (dbg != nullptr) {
+  float mt;
+  {
+    tmem_ld_x32(s_taddr + 0, &xr[0]);
+    tmem_ld_x32(s_taddr + 32, &xr[32]);
+    tc_wait_ld();
+    tmem_ld_x32(s_taddr + 64, &xr[64]);
+    tmem_ld_x32(s_taddr + 96, &xr[96]);
+    if (dbg != nullptr) {
 #pragma unroll
-    for (int i = 0; i < 64; ++i) dbg[kDbgS + i] = __uint_as_float(xr[i]);
-  }
-  const uint64_t scale2 = pack_f32x2(scale, scale);
-  float mxa = -INFINITY, mxb = -INFINITY;
-  if (kTcBias) max_half<0>(xr, mxa, mxb);
-  else         logits_half<0>(xr, bias_row, row7, scale2, mxa, mxb);
-  tc_wait_ld();
-  // the logits are in registers: hand the S buffer back so that the next Q K^T can start
-  tc_fence_before();
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::s_free + wg));
-  if (dbg != nullptr) {
+      for (int i = 0; i < 64; ++i) dbg[kDbgS + i] = __uint_as_float(xr[i]);
+    }
+    const uint64_t scale2 = pack_f32x2(scale, scale);
+    float mxa = -INFINITY, mxb = -INFINITY;
+    if (kTcBias) max_half<0>(xr, mxa, mxb);
+    else         logits_half<0>(xr, bias_row, row7, scale2, mxa, mxb);
+    tc_wait_ld();
+    // the logits are in registers: hand the S buffer back so that the next Q K^T can start
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_addr(c, BarIdx::s_free + wg));
+    if (dbg != nullptr) {
 #pragma unroll
-    for (int i = 64; i < kTile; ++i) dbg[kDbgS + i] = __uint_as_float(xr[i]);
+      for (int i = 64; i < kTile; ++i) dbg[kDbgS + i] = __uint_as_float(xr[i]);
+    }
+    if (kTcBias) max_half<64>(xr, mxa, mxb);
+    else         logits_half<64>(xr, bias_row, row7, scale2, mxa, mxb);
+    mt = fmaxf(mxa, mxb);
   }
-  if (kTcBias) max_half<64>(xr, mxa, mxb);
-  else         logits_half<64>(xr, bias_row, row7, scale2, mxa, mxb);
-
-  const float mt = fmaxf(mxa, mxb);
-  if (ts != nullptr) ts[2] = clock64() + (long long)(mt == 123.456f);   // after the logits pass
+  if (ts != nullptr) ts[2] = clock64() + (long long)(mt == 123.456f);   // logits and row maximum in registers
   // factor between a logit difference and the exponent of 2: log2(e), times the logit scale when
   // the tensor core's logits still lack it (fp8 q/k with tensor-core bias: `scale` carries it)
   const float ef = kTcBias ? scale : kLog2e;
@@ -692,25 +686,21 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
       alpha = ex2_approx((m_run - mt) * ef);
     }
   }
-  if (ts != nullptr) ts[3] = clock64();   // row maximum known
+  if (ts != nullptr) ts[3] = clock64();   // exponential pass starts
   // p = exp2((x - m) * log2e).  fp8 path: the subtraction comes first so that x == m gives
   // exactly 0 even for the huge negative values of masked keys (a row with no attended key: all
   // weights 1).  bf16 path: one fused multiply-add, x * log2e - m * log2e; for such a row x and
   // m are the same power of two, both products are exact and the result is 0 as well.
-  // What bounds this pass: a scheduler issues an ex2 over 8 cycles and no FMA-pipe instruction of
-  // any of its warps overlaps with that (measured), so a tile costs 128 x 8 cycles plus its
-  // FMA-pipe instructions, while ALU-pipe work (the maximum, the bf16 packing) is free.  The
-  // packed f32x2 forms halve the FMA-pipe instruction count at the same cost per value.
+  // The pass is one ex2 per logit on the XU (a warp-wide ex2 every 8 cycles per scheduler, shared
+  // by the scheduler's two softmax warps) with one packed FMA, one packed add and one bf16 pack per
+  // pair of logits around it.  The two warpgroups run their passes in step (2 000 - 2 500 cycles per
+  // pass against 2 048 for the XU alone); what keeps the kernel above that is the time between
+  // passes, when both read logits, search the maximum and hand P over and the XU idles.
   const uint64_t l2e2 = pack_f32x2(ef, ef);
   const uint64_t nm2 = pack_f32x2(-m_use, -m_use);
   const float nml = -m_use * ef;
   const uint64_t nml2 = pack_f32x2(nml, nml);
   uint64_t suma = pack_f32x2(0.f, 0.f), sumb = suma;
-  const uint64_t magic2 = pack_f32x2(kPolyMagic, kPolyMagic), nmagic2 = pack_f32x2(-kPolyMagic, -kPolyMagic);
-  const uint64_t mone2 = pack_f32x2(-1.f, -1.f);
-  const uint64_t pc0 = pack_f32x2(kPolyC0, kPolyC0), pc1 = pack_f32x2(kPolyC1, kPolyC1),
-                 pc2 = pack_f32x2(kPolyC2, kPolyC2), pc3 = pack_f32x2(kPolyC3, kPolyC3);
-  uint32_t hacc = 0;
   // The first kHeld column groups are computed before anything is written: the P buffer and the
   // O accumulator only become free when the previous P V of this warpgroup has finished, and that
   // wait is taken as late as the registers allow.
@@ -723,43 +713,13 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
       const int col = cidx * 16 + 2 * i;
       float y0, y1;
       const uint64_t x2 = pack_f32x2(__uint_as_float(xr[col]), __uint_as_float(xr[col + 1]));
-      const uint64_t y2 = kTcBias ? fma_f32x2(x2, l2e2, nml2) : mul_f32x2(add_f32x2(x2, nm2), l2e2);
-      unpack_f32x2(y2, y0, y1);
-      if (kExp == kExpF16x2) {
-        // two weights per XU instruction; their sum is taken from the rounded values, four words
-        // (eight keys) in f16, then widened
-        const uint32_t w = ex2_f16x2(pack_f16x2(y0, y1));
-        pk[cidx][i] = w;
-        if ((i & 3) == 0) hacc = w; else hacc = add_f16x2(hacc, w);
-        if ((i & 3) == 3) {
-          const uint64_t wide = f16x2_to_f32x2(hacc);
-          if (i & 4) sumb = add_f32x2(sumb, wide); else suma = add_f32x2(suma, wide);
-        }
-      } else if (kExp >= 1 && kExp <= 7 && i < kExp) {
-        // polynomial share.  y is at most kLazyRescaleLog2; below -126 the weight is zero (also for
-        // the -2^47 / -inf of masked and absent keys), which the clamp and the exponent add give:
-        // j = -126 and f = 0 leave 2^-126 * c0, and bf16 rounding of P drops nothing that matters
-        const uint64_t yc2 = pack_f32x2(fmaxf(y0, -126.0f), fmaxf(y1, -126.0f));
-        const uint64_t t2 = add_f32x2(yc2, magic2);              // magic + round(y)
-        const uint64_t f2 = fma_f32x2(add_f32x2(t2, nmagic2), mone2, yc2);   // y - round(y) in [-0.5, 0.5]
-        uint64_t q2 = fma_f32x2(pc3, f2, pc2);
-        q2 = fma_f32x2(q2, f2, pc1);
-        q2 = fma_f32x2(q2, f2, pc0);
-        float t0, t1, q0, q1;
-        unpack_f32x2(t2, t0, t1);
-        unpack_f32x2(q2, q0, q1);
-        const float p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
-        const float p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
-        if (i & 1) sumb = add_f32x2(sumb, pack_f32x2(p0, p1));
-        else       suma = add_f32x2(suma, pack_f32x2(p0, p1));
-        pk[cidx][i] = pack_bf16x2(p0, p1);
-      } else {
-        const float p0 = ex2_approx(y0);
-        const float p1 = ex2_approx(y1);
-        if (i & 1) sumb = add_f32x2(sumb, pack_f32x2(p0, p1));
-        else       suma = add_f32x2(suma, pack_f32x2(p0, p1));
-        pk[cidx][i] = pack_bf16x2(p0, p1);
-      }
+      if (kTcBias) unpack_f32x2(fma_f32x2(x2, l2e2, nml2), y0, y1);
+      else         unpack_f32x2(mul_f32x2(add_f32x2(x2, nm2), l2e2), y0, y1);
+      const float p0 = ex2_approx(y0);
+      const float p1 = ex2_approx(y1);
+      if (i & 1) sumb = add_f32x2(sumb, pack_f32x2(p0, p1));
+      else       suma = add_f32x2(suma, pack_f32x2(p0, p1));
+      pk[cidx][i] = pack_bf16x2(p0, p1);
     }
     if (dbg != nullptr) {
 #pragma unroll
@@ -786,6 +746,7 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
           tmem_st_x16(o_taddr + c0, o);
         }
       }
+      if (ts != nullptr) ts[5] = clock64();   // previous P V awaited
     }
     if (cidx >= kHeld - 1) {
       // P as bf16, two keys per 32-bit TMEM column: the A operand of the second GEMM
@@ -797,6 +758,7 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
                      : "memory");
     }
   }
+  if (ts != nullptr) ts[6] = clock64();     // last exponential issued
   tc_wait_st();
   if (ts != nullptr) ts[4] = clock64();   // P stored
   float s0, s1, s2, s3;
@@ -807,7 +769,7 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
   return true;
 }
 
-template <bool kDebug, bool kTcBias, int kExp>
+template <bool kDebug, bool kTcBias>
 __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
   const AttnParams& p = *c.p;
   const int row = wq * 32 + lane;                    // row of the 128-query tile == TMEM lane
@@ -856,9 +818,9 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
         float* dbg = nullptr;
         if (kDebug && p.debug != nullptr && blockIdx.x == 0 && icount == 0 && s == 0 && kt == 0)
           dbg = p.debug + (size_t)row * kTile;
-        if (!softmax_tile<kTcBias, kExp>(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row, row & 7, scale,
-                          kt == 0, ucnt > 0, BarIdx::kv_empty + (int)prev_stage, prev_round & 1, m_run,
-                          l_run, ts))
+        if (!softmax_tile<kTcBias>(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row, row & 7, scale,
+                                   kt == 0, ucnt > 0, BarIdx::kv_empty + (int)prev_stage, prev_round & 1, m_run,
+                                   l_run, ts))
           return;
         ++ucnt;
         {
@@ -931,7 +893,7 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
 }
 
 // ------------------------------------------------------------------ kernel
-template <bool kDebug, bool kTcBias, int kExp = kExpF32>
+template <bool kDebug, bool kTcBias>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ CUtensorMap tm_q,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -1011,13 +973,13 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
     } else if (warp == 1) {
       qk_issuer_role<kTcBias>(c);
     } else if (warp == 2) {
-      pv_issuer_role<kTcBias, kExp>(c, lane);
+      pv_issuer_role<kTcBias>(c, lane);
     } else if (warp == 3) {
       if (p.mask_col) mask_writer_role(c, lane);
     }
   } else {
     setmaxnreg_inc<kRegsSoftmax>();
-    softmax_role<kDebug, kTcBias, kExp>(c, (warp - 4) >> 2, warp & 3, lane);
+    softmax_role<kDebug, kTcBias>(c, (warp - 4) >> 2, warp & 3, lane);
   }
 
   tc_fence_before();

@@ -1,0 +1,242 @@
+// The four input projections of the grid / triangle attention block as ONE pass over the
+// (layer-normed) pair representation, for sm_100a:
+//
+//     [q | k | v | gate] = x [M, 128] * W4^T,     W4 = [Wq; Wk; Wv; Wg]  ([512, 128], rows = output channels)
+//
+// Stands in for the per-(row, head) K/V projection BRGEMMs and the per-query-block Q and gate
+// projection BRGEMMs of the reference's fused block (src/csrc/dot_product_attention.cpp:285-298
+// and :300-338).  x is read once (the reference, and four separate GEMMs, read it four times);
+// q, k and v leave in the head-major layout [R, H, N, D] the attention kernel's TMA reads with
+// unit-stride rows, q already multiplied by the softmax scale (in fp32, rounded once); the gate
+// leaves as [M, 128].  HBM-bound: 256 bytes read and 1024 written per row of x.
+//
+//   warp 0      TMA producer: W4 once (128 KB, stays in shared memory), then x tiles of 128 rows
+//   warp 1      allocates TMEM, issues tcgen05.mma: per x tile two groups of 8 (N = 256, K = 16),
+//               columns [0, 256) = q | k and [256, 512) = v | gate
+//   warps 4-7   epilogue of columns [0, 256): TMEM -> registers -> bf16 -> global
+//   warps 8-11  epilogue of columns [256, 512)
+// The two column halves have their own full / empty barriers, so the MMAs of one half run while
+// the other half is being drained.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "ptx_sm100.cuh"
+
+namespace af3k {
+
+constexpr int kProjC = 128;                 // input channels (c_pair)
+constexpr int kProjOut = 4 * kProjC;        // q | k | v | gate
+constexpr int kProjThreads = 384;
+constexpr int kProjStages = 2;              // x tiles in flight
+constexpr uint32_t kProjXTileBytes = 128 * kProjC * 2;          // 32 KB: two 128B-swizzled panels of 64 channels
+constexpr uint32_t kProjWBytes = kProjOut * kProjC * 2;         // 128 KB: two panels of 64 channels x 512 rows
+constexpr uint32_t kProjSmemBytes = kProjWBytes + kProjStages * kProjXTileBytes + 256 /*barriers*/ + 1024 /*alignment*/;
+
+struct ProjParams {
+  long long M;           // rows of x (= R * N)
+  int N;                 // tokens per pair row
+  int H, D;              // heads and head width, H * D == 128
+  float q_scale;         // applied to the q columns before rounding
+  __nv_bfloat16* q;      // [R, H, N, D]
+  __nv_bfloat16* k;
+  __nv_bfloat16* v;
+  __nv_bfloat16* g;      // [M, 128]
+  int* status;           // same status word as the attention kernel
+  long long wait_limit;
+};
+
+struct ProjBar {
+  static constexpr int w_full = 0;
+  static constexpr int x_full = 1;                       // [kProjStages]
+  static constexpr int x_empty = 1 + kProjStages;        // [kProjStages]
+  static constexpr int acc_full = 1 + 2 * kProjStages;   // [2] column halves
+  static constexpr int acc_empty = 3 + 2 * kProjStages;  // [2]
+  static constexpr int count = 5 + 2 * kProjStages;
+};
+
+__device__ __forceinline__ void proj_timeout(const ProjParams& p, volatile int* abort_flag, int bar) {
+  *abort_flag = 1;
+  if (p.status != nullptr) {
+    atomicOr(p.status, 1 /* wait timeout */);
+    if (atomicCAS(p.status + 1, 0, 1000 + bar + 1) == 0) {
+      p.status[2] = blockIdx.x;
+      p.status[3] = threadIdx.x >> 5;
+    }
+  }
+}
+
+#define AF3K_PROJ_WAIT(idx, parity)                                                              \
+  do {                                                                                           \
+    const bool ok_ = mbar_wait_bounded(bars + 8u * (idx), (parity), p.wait_limit, &abort_flag);   \
+    if (!__all_sync(0xffffffffu, ok_)) {                                                         \
+      proj_timeout(p, &abort_flag, (idx));                                                       \
+      goto done;                                                                                 \
+    }                                                                                            \
+  } while (0)
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kProjThreads, 1)
+qkvg_projection_kernel(const __grid_constant__ ProjParams p, const __grid_constant__ CUtensorMap tm_x,
+                       const __grid_constant__ CUtensorMap tm_w) {
+  extern __shared__ uint8_t proj_smem_raw[];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem = (smem_u32(proj_smem_raw) + 1023u) & ~1023u;
+  const uint32_t w_smem = smem;                                   // [2 panels][512 rows][128 B]
+  const uint32_t x_smem = smem + kProjWBytes;                     // [stages][2 panels][128 rows][128 B]
+  const uint32_t bars = x_smem + kProjStages * kProjXTileBytes;
+  const long long n_tiles = (p.M + 127) / 128;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    prefetch_tensormap(&tm_x);
+    prefetch_tensormap(&tm_w);
+    mbar_init(bars + 8u * ProjBar::w_full, 1);
+    for (int i = 0; i < kProjStages; ++i) {
+      mbar_init(bars + 8u * (ProjBar::x_full + i), 1);
+      mbar_init(bars + 8u * (ProjBar::x_empty + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bars + 8u * (ProjBar::acc_full + i), 1);
+      mbar_init(bars + 8u * (ProjBar::acc_empty + i), 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_slot;
+
+  if (warp == 0) {
+    // ---- producer (whole warp runs the control flow, one lane issues)
+    const bool leader = elect_one();
+    if (leader) {
+      mbar_arrive_expect_tx(bars + 8u * ProjBar::w_full, kProjWBytes);
+      for (int kb = 0; kb < 2; ++kb)
+        for (int nb = 0; nb < 2; ++nb)
+          tma_load_2d(w_smem + kb * (kProjWBytes / 2) + nb * 256 * 128, &tm_w, bars + 8u * ProjBar::w_full, kb * 64, nb * 256);
+    }
+    uint32_t n = 0;
+    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++n) {
+      const uint32_t st = n % kProjStages;
+      if (n >= kProjStages) AF3K_PROJ_WAIT(ProjBar::x_empty + st, ((n / kProjStages) - 1) & 1);
+      if (leader) {
+        const uint32_t full = bars + 8u * (ProjBar::x_full + st);
+        const uint32_t dst = x_smem + st * kProjXTileBytes;
+        mbar_arrive_expect_tx(full, kProjXTileBytes);
+        tma_load_2d(dst, &tm_x, full, 0, (int)(tile * 128));
+        tma_load_2d(dst + kProjXTileBytes / 2, &tm_x, full, 64, (int)(tile * 128));
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer
+    const bool leader = elect_one();
+    const uint32_t idesc = make_idesc(1u, 1u, 0u, 0u, 256);
+    const uint64_t ad0 = make_smem_desc(x_smem, 16, 8 * 128, 2);
+    const uint64_t bd0 = make_smem_desc(w_smem, 16, 8 * 128, 2);
+    const uint32_t ad_lo = (uint32_t)ad0, ad_hi = (uint32_t)(ad0 >> 32);
+    const uint32_t bd_lo = (uint32_t)bd0, bd_hi = (uint32_t)(bd0 >> 32);
+    AF3K_PROJ_WAIT(ProjBar::w_full, 0);
+    uint32_t n = 0;
+    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++n) {
+      const uint32_t st = n % kProjStages;
+      AF3K_PROJ_WAIT(ProjBar::x_full + st, (n / kProjStages) & 1);
+      for (int nh = 0; nh < 2; ++nh) {
+        // the epilogue warps of this half must have read the previous tile's columns
+        if (n >= 1) AF3K_PROJ_WAIT(ProjBar::acc_empty + nh, (n - 1) & 1);
+        tc_fence_after();
+        if (leader) {
+#pragma unroll
+          for (int ks = 0; ks < kProjC / 16; ++ks) {
+            // 16 channels = 32 bytes of a 128-byte panel row; panel ks / 4
+            const uint32_t a = ad_lo + ((st * kProjXTileBytes + (ks >> 2) * (kProjXTileBytes / 2)) >> 4) + 2 * (ks & 3);
+            const uint32_t b = bd_lo + (((ks >> 2) * (kProjWBytes / 2) + nh * 256 * 128) >> 4) + 2 * (ks & 3);
+            mma_ss_f16(tmem + nh * 256, a, ad_hi, b, bd_hi, idesc, ks > 0 ? 1u : 0u);
+          }
+          tc_commit(bars + 8u * (ProjBar::acc_full + nh));
+          if (nh == 1) tc_commit(bars + 8u * (ProjBar::x_empty + st));
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp >= 4) {
+    // ---- epilogue: warp quarter (TMEM lanes) x column half
+    const int quarter = warp & 3, half = (warp - 4) >> 2;
+    const uint32_t t_base = tmem + ((uint32_t)(quarter * 32) << 16) + half * 256;
+    uint32_t n = 0;
+    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++n) {
+      AF3K_PROJ_WAIT(ProjBar::acc_full + half, n & 1);
+      tc_fence_after();
+      const long long m = tile * 128 + quarter * 32 + lane;          // this thread's row of x
+      const bool valid = m < p.M;
+      const long long r = m / p.N;
+      const int tok = (int)(m - r * p.N);
+#pragma unroll 1
+      for (int c0 = 0; c0 < 256; c0 += 64) {
+        uint32_t acc[64];
+        tmem_ld_x32(t_base + c0, &acc[0]);
+        tmem_ld_x32(t_base + c0 + 32, &acc[32]);
+        tc_wait_ld();
+        if (c0 == 192) {
+          // the last columns are in registers: the MMAs of the next tile may overwrite this half
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + 8u * (ProjBar::acc_empty + half));
+        }
+        if (valid) {
+          const int col0 = half * 256 + c0;                           // 64 columns of one output tensor
+          const int which = col0 >> 7, within = col0 & 127;           // 0 q, 1 k, 2 v, 3 gate
+          const float mul = which == 0 ? p.q_scale : 1.0f;
+#pragma unroll
+          for (int j = 0; j < 64; j += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(acc[j + 0]) * mul, __uint_as_float(acc[j + 1]) * mul);
+            o.y = pack_bf16x2(__uint_as_float(acc[j + 2]) * mul, __uint_as_float(acc[j + 3]) * mul);
+            o.z = pack_bf16x2(__uint_as_float(acc[j + 4]) * mul, __uint_as_float(acc[j + 5]) * mul);
+            o.w = pack_bf16x2(__uint_as_float(acc[j + 6]) * mul, __uint_as_float(acc[j + 7]) * mul);
+            const int ch = within + j;
+            if (which == 3) {
+              *reinterpret_cast<uint4*>(p.g + m * kProjC + ch) = o;
+            } else {
+              __nv_bfloat16* base = which == 0 ? p.q : (which == 1 ? p.k : p.v);
+              const int head = ch / p.D, d = ch - head * p.D;
+              *reinterpret_cast<uint4*>(base + ((r * p.H + head) * p.N + tok) * p.D + d) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag != 0) {
+    for (int i = 0; i < 200; ++i) __nanosleep(10000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace af3k

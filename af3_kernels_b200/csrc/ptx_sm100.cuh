@@ -237,6 +237,15 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t* r) {
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+      ::AF3K_W8(r, 0), AF3K_W8(r, 8), AF3K_W8(r, 16), AF3K_W8(r, 24), "r"(taddr)
+      : "memory");
+}
+
 // Register budget hand-over between warpgroups (all 128 threads of the warpgroup execute it).
 template <int kRegs>
 __device__ __forceinline__ void setmaxnreg_inc() {
@@ -281,37 +290,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-// Packed half precision: two exponentials per XU instruction.
-__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
-  uint32_t y;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
-// packs {lo, hi} -> f16x2 with lo in bits [0,16)
-__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-__device__ __forceinline__ uint32_t add_f16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-__device__ __forceinline__ uint64_t f16x2_to_f32x2(uint32_t h2) {
-  uint64_t r;
-  asm("{\n\t"
-      ".reg .b16 lo, hi;\n\t"
-      ".reg .f32 flo, fhi;\n\t"
-      "mov.b32 {lo, hi}, %1;\n\t"
-      "cvt.f32.f16 flo, lo;\n\t"
-      "cvt.f32.f16 fhi, hi;\n\t"
-      "mov.b64 %0, {flo, fhi};\n\t"
-      "}\n"
-      : "=l"(r)
-      : "r"(h2));
-  return r;
 }
 // packs {lo, hi} -> bf16x2 with lo in bits [0,16)
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

@@ -56,27 +56,13 @@ def stage_bias(bias: torch.Tensor, B2: int, Sq: int, Sk: int, *, q_scale=None, k
     ``softmax_scale * q_scale[h] * k_scale[h]``, default scale ``1/sqrt(head_dim)``)."""
     if not bias.is_cuda:
         raise RuntimeError("af3_kernels_b200 runs on CUDA tensors only (no CPU fallback)")
-    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
-    prescaled = False
-    if not isinstance(bias, StagedBias):
-        if bias.numel() != B2 * Sq * Sk:
-            raise ValueError(f"bias must have B2*Sq*Sk = {B2 * Sq * Sk} elements, got {bias.numel()}")
-        needs_copy = (bias.dtype != torch.bfloat16 or bias.dim() != 3 or bias.stride(-1) != 1
-                      or (bias.stride(-2) * 2) % 16 != 0 or (bias.stride(0) * 2) % 16 != 0
-                      or bias.data_ptr() % 16 != 0)
-        if use_workspace and cache_bias and (needs_copy or fp8):
-            bias = _cached_stage(bias, B2, Sq, Sk, D, q_scale if fp8 else None, k_scale if fp8 else None, scale)
-    if isinstance(bias, StagedBias):
-        if (bias.B2, bias.Sq, bias.Sk) != (B2, Sq, Sk) or bias.prescaled != fp8:
-            raise ValueError("staged bias was made for another shape or another q/k type")
-        prescaled = bias.prescaled
-        bias = bias.data[:, :, :Sk]
-    else:
-        if bias.dtype not in (torch.bfloat16, torch.float32):
-            bias = bias.to(torch.float32)
-        bias = bias.reshape(B2, Sq, Sk) if bias.dim() != 3 else bias
-        if (Sk > 1 and bias.stride(2) != 1) or (B2 > 1 and bias.stride(0) == 0) or (Sq > 1 and bias.stride(1) == 0):
-            bias = bias.contiguous()
+    if bias.numel() != B2 * Sq * Sk:
+        raise ValueError(f"bias must have B2*Sq*Sk = {B2 * Sq * Sk} elements, got {bias.numel()}")
+    if bias.dtype not in (torch.bfloat16, torch.float32):
+        bias = bias.to(torch.float32)
+    bias = bias.reshape(B2, Sq, Sk) if bias.dim() != 3 else bias
+    if (Sk > 1 and bias.stride(2) != 1) or (B2 > 1 and bias.stride(0) == 0) or (Sq > 1 and bias.stride(1) == 0):
+        bias = bias.contiguous()
     fp8 = q_scale is not None
     desc = _capi.AttentionDesc()
     desc.B1, desc.B2, desc.Sq, desc.Sk, desc.D = 1, B2, Sq, Sk, 16 * ((head_dim + 15) // 16)

@@ -7,10 +7,11 @@
 * ``self_attention_block`` stands in for ``_C.self_attention`` (:380-543, wrapper :83-105): single /
   diffusion attention over one token sequence with a query bias and gating, no output projection.
 
-The projections are plain GEMMs and go through torch (cuBLAS); the core is the hand-written kernel
-behind ``libaf3k.so``.  q, k and v are never rearranged in memory: the ``[.., N, H*D]`` projection
-outputs are handed to the kernel as strided ``[.., H, N, D]`` views, and the kernel writes its
-result straight into the ``[.., N, H*D]`` layout the gating needs.
+For the grid block at c_pair = 128 the four input projections are one hand-written pass over the
+pair (``af3k_qkvg_projection``: q, k, v leave head-major and q pre-scaled); the output projection
+is a plain GEMM through torch (cuBLAS), as are all projections of other widths, whose
+``[.., N, H*D]`` outputs are handed to the attention kernel as strided ``[.., H, N, D]`` views.  The
+kernel writes its result straight into the ``[.., N, H*D]`` layout the gating needs.
 
 Weights are taken the way the reference passes them: ``[in_features, out_features]``
 (``linear.weight.T.contiguous()``; the reference additionally VNNI-repacks them for its CPU GEMM,
@@ -22,8 +23,10 @@ from typing import Optional
 
 import torch
 
+import ctypes
+
 from . import _capi
-from .dpa import dot_product_attention
+from .dpa import _status_buffer, dot_product_attention
 
 
 def _as_bf16(t: torch.Tensor) -> torch.Tensor:
@@ -45,6 +48,45 @@ def sigmoid_gate(weighted: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
         _capi.check(_capi.load().af3k_sigmoid_gate(weighted.data_ptr(), gate.data_ptr(), out.data_ptr(), n,
                                                    torch.cuda.current_stream().cuda_stream))
     return out
+
+
+_w4_cache: dict = {}
+
+
+def _stacked_projection_weights(q_proj, k_proj, v_proj, gating_query) -> torch.Tensor:
+    """[512, 128] bf16: the four [in, out] projection weights as stacked [out, in] rows (q, k, v,
+    gate), which is the K-major B operand the projection kernel reads.  Built once per set of
+    weight tensors (keyed by their storage and version)."""
+    key = tuple((w.data_ptr(), w._version, w.dtype, tuple(w.stride())) for w in (q_proj, k_proj, v_proj, gating_query))
+    w4 = _w4_cache.get(key)
+    if w4 is None:
+        if len(_w4_cache) >= 16:
+            _w4_cache.clear()
+        w4 = torch.cat([_as_bf16(w.detach()).t() for w in (q_proj, k_proj, v_proj, gating_query)], dim=0).contiguous()
+        _w4_cache[key] = w4
+    return w4
+
+
+def qkvg_projection(x: torch.Tensor, w4: torch.Tensor, head: int, q_scale: float):
+    """x [R, N, 128] bf16 contiguous, w4 [512, 128] bf16 -> (q, k, v [R, head, N, 128 / head], gate
+    [R, N, 128]), all bf16, q pre-multiplied by ``q_scale`` (``af3k_qkvg_projection``)."""
+    R, N, C = x.shape
+    D = C // head
+    q = torch.empty((R, head, N, D), dtype=torch.bfloat16, device=x.device)
+    k = torch.empty_like(q)
+    v = torch.empty_like(q)
+    g = torch.empty((R, N, C), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        _capi.check(_capi.load().af3k_qkvg_projection(
+            x.data_ptr(), w4.data_ptr(), R, N, head, ctypes.c_float(q_scale), q.data_ptr(), k.data_ptr(),
+            v.data_ptr(), g.data_ptr(), _status_buffer(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return q, k, v, g
+
+
+def _fused_projection_ok(x: torch.Tensor, head: int) -> bool:
+    C = x.shape[-1]
+    return (C == 128 and C % head == 0 and (C // head) % 8 == 0 and x.dtype == torch.bfloat16
+            and x.is_contiguous() and x.data_ptr() % 16 == 0 and x.numel() > 0)
 
 
 def attention_block(
@@ -69,6 +111,15 @@ def attention_block(
         raise ValueError("c_pair must be divisible by the number of heads")
     D = C // head
     x = _as_bf16(pair)
+    if _fused_projection_ok(x, head):
+        # c_pair = 128: one pass over x for all four projections; q, k, v leave head-major with q
+        # already scaled, so the attention core reads unit-stride rows and scales nothing
+        w4 = _stacked_projection_weights(q_proj, k_proj, v_proj, gating_query)
+        q, k, v, gate = qkvg_projection(x, w4, head, D ** -0.5)
+        weighted = torch.empty((R, N, head, D), dtype=torch.bfloat16, device=pair.device)
+        dot_product_attention(q, k, v, mask, bias, softmax_scale=1.0, out=weighted.permute(0, 2, 1, 3))
+        gated = sigmoid_gate(weighted.view(R, N, C), gate)
+        return torch.matmul(gated, _as_bf16(out_proj)).to(pair.dtype)
     q = torch.matmul(x, _as_bf16(q_proj)).view(R, N, head, D).permute(0, 2, 1, 3)
     k = torch.matmul(x, _as_bf16(k_proj)).view(R, N, head, D).permute(0, 2, 1, 3)
     v = torch.matmul(x, _as_bf16(v_proj)).view(R, N, head, D).permute(0, 2, 1, 3)

@@ -385,6 +385,7 @@ def row_sharded_report(args, O, dev, world, rank):
         "E2": t1_ms / (world * total_ms), "E2_with_bcast": t1_ms / (world * (total_ms + bcast_ms)),
         "gather_inbound_bytes_per_gpu": inbound, "gather_floor_ms": floor_ms,
         "gather_floor_basis": f"{NVLINK_GBS_PER_DIRECTION:.0f} GB/s per direction per GPU (nominal NVLink 5)",
+        "gather_floor_ms_at_770_gbs": inbound / 770e9 * 1e3,
         "comm_split": sharder.comm_split, "sharded_equals_single": bool(eq.item() == 1),
         "definitions": "E1 = t1 / (N * slowest rank's kernel on its row block); E2 = t1 / (N * time of "
                        "RowShardedAttention.forward: kernel pieces + chunked NCCL all-gather on a side stream)",

@@ -188,6 +188,24 @@ int af3k_pair_bias(const void* pair, int32_t pair_dtype, int64_t R, int64_t N, i
                    const float* gamma, const float* beta, const float* proj, float eps, void* normed,
                    void* bias, int64_t bias_pitch, void* stream);
 
+/* The four input projections of the grid / triangle attention block in one pass over the
+ * layer-normed pair representation (c_pair = 128):  [q | k | v | gate] = x * W4^T.
+ *
+ * Stands in for the K / V projection BRGEMMs per (pair row, head) and the Q and gate projection
+ * BRGEMMs per query block inside the reference's fused block
+ * (src/csrc/dot_product_attention.cpp:285-298 and :300-338).
+ *
+ *   x     [R, N, 128] bf16, contiguous
+ *   w4    [512, 128] bf16: the four nn.Linear weights (out x in) stacked in the order q, k, v, gate
+ *   q,k,v [R, H, N, 128 / H] bf16, contiguous (what af3k_dot_product_attention reads with unit-stride
+ *         rows); q is multiplied by q_scale in fp32 before it is rounded, so the attention call
+ *         that follows passes softmax_scale = 1
+ *   gate  [R, N, 128] bf16
+ * H must divide 128 with 128 / H a multiple of 8.  All pointers 16-byte aligned.  status_dev as in
+ * af3k_dot_product_attention (may be NULL).  stream is a cudaStream_t. */
+int af3k_qkvg_projection(const void* x, const void* w4, int64_t R, int64_t N, int64_t H, float q_scale,
+                         void* q, void* k, void* v, void* gate, int* status_dev, void* stream);
+
 /* out = weighted * sigmoid(gate), elementwise over n bf16 elements (n a multiple of 8; all three
  * pointers 16-byte aligned; out may be weighted).  Stands in for the SigmoidFwdTPP + MulTPP pair
  * behind the attention core in the reference's fused blocks

@@ -114,3 +114,30 @@ def test_distributed_module_single_rank_equals_plain_module(cuda_device, blocks)
         assert (a - b).abs().max().item() <= 2e-2 * a.abs().max().item()
     finally:
         dist.destroy_process_group()
+
+
+def test_fused_projection_kernel_matches_plain_gemms(cuda_device):
+    """af3k_qkvg_projection: q, k, v head-major with q pre-scaled, gate row-major, against fp32
+    matmuls of the same bf16 operands (bf16 rounding of the result only), on a ragged row count and
+    for every head count the kernel takes."""
+    from af3_kernels_b200.fused_ops import _stacked_projection_weights, qkvg_projection
+    from af3_kernels_b200.dpa import read_status
+    dev = cuda_device
+    g = torch.Generator().manual_seed(3)
+    for R, N, H in ((3, 200, 4), (1, 37, 2), (2, 129, 16), (5, 256, 8)):
+        C, D = 128, 128 // H
+        x = torch.randn(R, N, C, generator=g).to(torch.bfloat16).to(dev)
+        ws = [(torch.randn(C, C, generator=g) * 0.1).to(torch.bfloat16).to(dev) for _ in range(4)]   # [in, out]
+        w4 = _stacked_projection_weights(*ws)
+        assert w4.shape == (4 * C, C)
+        scale = D ** -0.5
+        q, k, v, gate = qkvg_projection(x, w4, H, scale)
+        torch.cuda.synchronize()
+        assert read_status(dev)[0] == 0
+        ref = [x.float() @ w.float() for w in ws]
+        ref[0] = ref[0] * scale
+        for got, want in zip((q, k, v), ref[:3]):
+            want = want.view(R, N, H, D).permute(0, 2, 1, 3)
+            assert got.shape == want.shape
+            assert (got.float() - want).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item()), (R, N, H)
+        assert (gate.float() - ref[3]).abs().max().item() <= 2e-2 * max(1.0, ref[3].abs().max().item())
