@@ -64,8 +64,9 @@ class DistributedGridSelfAttentionCpp(GridSelfAttentionCpp):
     """Reference: src/af3_kernels/Attention.py:85-203.  Every rank holds the whole ``pair`` and
     computes the rows ``[rank * ceil(N / ws), (rank + 1) * ceil(N / ws))``; the bias is computed
     redundantly on every rank from the replicated pair, the mask is sliced by row, and the row
-    blocks are all-gathered in ``COMM_SPLIT`` pieces.  The reference overlaps gather *i* with the
-    compute of piece *i + 1* from a helper thread; here the gather runs on a side CUDA stream."""
+    blocks are exchanged in ``COMM_SPLIT`` pieces.  The reference overlaps gather *i* with the
+    compute of piece *i + 1* from a helper thread; here the exchange (one in-place broadcast per rank
+    and piece) runs on a side CUDA stream."""
 
     def __init__(self, c_pair: int = 128, num_head: int = 4, transpose: bool = False):
         super().__init__(c_pair, num_head, transpose)
@@ -93,18 +94,18 @@ class DistributedGridSelfAttentionCpp(GridSelfAttentionCpp):
         start = time.time()
         for begin in range(0, split_size, piece):
             end = min(split_size, begin + piece)
-            out = attention_block(chunk[begin:end], local_mask[begin:end], bias, *self._weights(),
-                                  self.num_head).contiguous()
-            buf = torch.empty((ws, end - begin, *pair.shape[1:]), device=pair.device, dtype=pair.dtype)
+            # this rank's piece goes straight into its slot of the result; the other ranks' pieces
+            # arrive in place, one broadcast per rank, on the side stream
+            gathered[rk, begin:end].copy_(attention_block(chunk[begin:end], local_mask[begin:end], bias,
+                                                          *self._weights(), self.num_head))
             ready = torch.cuda.Event()
             ready.record(torch.cuda.current_stream(pair.device))
             with torch.cuda.stream(self._comm_stream):
                 self._comm_stream.wait_event(ready)
-                dist.all_gather_into_tensor(buf.view(-1, *pair.shape[1:]), out)
-                gathered[:, begin:end].copy_(buf)
-                out.record_stream(self._comm_stream)
-                buf.record_stream(self._comm_stream)
+                for r in range(ws):
+                    dist.broadcast(gathered[r, begin:end], src=r)
         torch.cuda.current_stream(pair.device).wait_stream(self._comm_stream)
+        gathered.record_stream(self._comm_stream)
         record_comm_time("AG Attn", time.time() - start,
                          gathered.numel() * gathered.element_size() * (ws - 1) / ws)
 

@@ -13,8 +13,12 @@
 //   warp 0      TMA producer: W4 once (128 KB, stays in shared memory), then x tiles of 128 rows
 //   warp 1      allocates TMEM, issues tcgen05.mma: per x tile two groups of 8 (N = 256, K = 16),
 //               columns [0, 256) = q | k and [256, 512) = v | gate
-//   warps 4-7   epilogue of columns [0, 256): TMEM -> registers -> bf16 -> global
+//   warps 4-7   epilogue of columns [0, 256): TMEM -> registers -> bf16 -> shared -> global
 //   warps 8-11  epilogue of columns [256, 512)
+// A TMEM lane is a row of x, so a thread holds 64 consecutive output columns of ONE row; stored
+// from there, a warp's 16-byte pieces would land 64 or 256 bytes apart.  Each epilogue warp
+// therefore passes its 32 rows x 128 bytes through a private, XOR-swizzled patch of shared memory
+// and stores with consecutive lanes on consecutive 16-byte pieces (full 64 / 128-byte runs).
 // The two column halves have their own full / empty barriers, so the MMAs of one half run while
 // the other half is being drained.
 #pragma once
@@ -33,7 +37,9 @@ constexpr int kProjThreads = 384;
 constexpr int kProjStages = 2;              // x tiles in flight
 constexpr uint32_t kProjXTileBytes = 128 * kProjC * 2;          // 32 KB: two 128B-swizzled panels of 64 channels
 constexpr uint32_t kProjWBytes = kProjOut * kProjC * 2;         // 128 KB: two panels of 64 channels x 512 rows
-constexpr uint32_t kProjSmemBytes = kProjWBytes + kProjStages * kProjXTileBytes + 256 /*barriers*/ + 1024 /*alignment*/;
+constexpr uint32_t kProjStagingBytes = 8 * 32 * 128;            // per epilogue warp: 32 rows x 64 bf16 columns
+constexpr uint32_t kProjSmemBytes = kProjWBytes + kProjStages * kProjXTileBytes + 256 /*barriers*/ +
+                                    kProjStagingBytes + 1024 /*alignment*/;
 
 struct ProjParams {
   long long M;           // rows of x (= R * N)
@@ -181,14 +187,15 @@ qkvg_projection_kernel(const __grid_constant__ ProjParams p, const __grid_consta
     // ---- epilogue: warp quarter (TMEM lanes) x column half
     const int quarter = warp & 3, half = (warp - 4) >> 2;
     const uint32_t t_base = tmem + ((uint32_t)(quarter * 32) << 16) + half * 256;
+    const uint32_t patch = bars + 256 + (uint32_t)(warp - 4) * (32 * 128);
+    const int log2d = 31 - __clz(p.D);
     uint32_t n = 0;
     for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++n) {
       AF3K_PROJ_WAIT(ProjBar::acc_full + half, n & 1);
       tc_fence_after();
-      const long long m = tile * 128 + quarter * 32 + lane;          // this thread's row of x
-      const bool valid = m < p.M;
-      const long long r = m / p.N;
-      const int tok = (int)(m - r * p.N);
+      const long long m0 = tile * 128 + quarter * 32;                 // the warp's first row of x
+      const long long r0 = m0 / p.N;
+      const int tok0 = (int)(m0 - r0 * p.N);
 #pragma unroll 1
       for (int c0 = 0; c0 < 256; c0 += 64) {
         uint32_t acc[64];
@@ -201,27 +208,44 @@ qkvg_projection_kernel(const __grid_constant__ ProjParams p, const __grid_consta
           __syncwarp();
           if (lane == 0) mbar_arrive(bars + 8u * (ProjBar::acc_empty + half));
         }
-        if (valid) {
-          const int col0 = half * 256 + c0;                           // 64 columns of one output tensor
-          const int which = col0 >> 7, within = col0 & 127;           // 0 q, 1 k, 2 v, 3 gate
-          const float mul = which == 0 ? p.q_scale : 1.0f;
+        const int col0 = half * 256 + c0;                             // 64 columns of one output tensor
+        const int which = col0 >> 7, within = col0 & 127;             // 0 q, 1 k, 2 v, 3 gate
+        const float mul = which == 0 ? p.q_scale : 1.0f;
+        // own row -> shared, piece j at position j ^ (row & 7): conflict-free both ways
 #pragma unroll
-          for (int j = 0; j < 64; j += 8) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(acc[j + 0]) * mul, __uint_as_float(acc[j + 1]) * mul);
-            o.y = pack_bf16x2(__uint_as_float(acc[j + 2]) * mul, __uint_as_float(acc[j + 3]) * mul);
-            o.z = pack_bf16x2(__uint_as_float(acc[j + 4]) * mul, __uint_as_float(acc[j + 5]) * mul);
-            o.w = pack_bf16x2(__uint_as_float(acc[j + 6]) * mul, __uint_as_float(acc[j + 7]) * mul);
-            const int ch = within + j;
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t w0 = pack_bf16x2(__uint_as_float(acc[8 * j + 0]) * mul, __uint_as_float(acc[8 * j + 1]) * mul);
+          const uint32_t w1 = pack_bf16x2(__uint_as_float(acc[8 * j + 2]) * mul, __uint_as_float(acc[8 * j + 3]) * mul);
+          const uint32_t w2 = pack_bf16x2(__uint_as_float(acc[8 * j + 4]) * mul, __uint_as_float(acc[8 * j + 5]) * mul);
+          const uint32_t w3 = pack_bf16x2(__uint_as_float(acc[8 * j + 6]) * mul, __uint_as_float(acc[8 * j + 7]) * mul);
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 128 + ((j ^ (lane & 7)) << 4)),
+                       "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+        }
+        __syncwarp();
+        // shared -> global: lane l takes piece l & 7 of rows l >> 3, l >> 3 + 4, ...
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int row = it * 4 + (lane >> 3), j = lane & 7;
+          uint4 o;
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w)
+                       : "r"(patch + row * 128 + ((j ^ (row & 7)) << 4)));
+          const long long m = m0 + row;
+          if (m < p.M) {
+            const int ch = within + 8 * j;
             if (which == 3) {
               *reinterpret_cast<uint4*>(p.g + m * kProjC + ch) = o;
             } else {
+              long long r = r0;
+              int tok = tok0 + row;
+              while (tok >= p.N) { tok -= p.N; ++r; }
               __nv_bfloat16* base = which == 0 ? p.q : (which == 1 ? p.k : p.v);
-              const int head = ch / p.D, d = ch - head * p.D;
-              *reinterpret_cast<uint4*>(base + ((r * p.H + head) * p.N + tok) * p.D + d) = o;
+              const int head = ch >> log2d, d = ch & (p.D - 1);
+              *reinterpret_cast<uint4*>(base + (((r * p.H + head) * p.N + tok) << log2d) + d) = o;
             }
           }
         }
+        __syncwarp();      // the patch is rewritten by the next 64 columns
       }
     }
   }

@@ -4,10 +4,10 @@ Every (pair row, head) is an independent attention problem, so the rows of the p
 representation are split into contiguous blocks, one per rank, exactly as the reference's
 ``DistributedGridSelfAttentionCpp`` does (src/af3_kernels/Attention.py:145-156): rank ``r`` owns
 rows ``[r * ceil(rows / ws), (r + 1) * ceil(rows / ws))``; the bias is replicated and the mask is
-sliced by row.  No collective sits on the data path of the kernel.  The optional output
-all-gather is cut into ``comm_split`` pieces and issued on a side stream, so the gather of piece
+sliced by row.  No collective sits on the data path of the kernel.  The optional gather of the
+output is cut into ``comm_split`` pieces and issued on a side stream, so the exchange of piece
 ``i`` overlaps the kernel of piece ``i + 1`` (the reference does this with a helper thread and a
-queue, Attention.py:162-195).
+queue around ``dist.all_gather``, Attention.py:162-195).
 """
 from __future__ import annotations
 
@@ -42,6 +42,8 @@ class RowShardedAttention:
             raise ValueError("comm_split must be >= 1")
         self.group = group
         self.comm_split = comm_split
+        # the CUDA operator writes into a caller-provided ``out``; a stand-in (CPU tests) returns its result
+        self.writes_in_place = attention_fn is None
         if attention_fn is None:
             from .dpa import dot_product_attention as attention_fn
         self.attention_fn = attention_fn
@@ -77,7 +79,13 @@ class RowShardedAttention:
 
     def forward(self, q, k, v, mask, bias, rows: int, timeout_s: float = 60.0) -> torch.Tensor:
         """q, k, v, mask: this rank's row block (``shard`` of the full tensors).  Returns the
-        full ``[rows, H, N, D]`` output on every rank."""
+        full ``[rows, H, N, D]`` output on every rank.
+
+        The result buffer is laid out ``[rank, row in block, H, N, D]``, which is the row order of
+        the full problem, so every rank computes each piece of its block straight into its own
+        slot and the pieces of the other ranks arrive in place: per piece one broadcast per rank
+        (each rank is the root of its own slot), issued on a side stream while the next piece is
+        computed.  Nothing is copied after the collective."""
         ws, rank = self.world_size, self.rank
         b, e, split = row_partition(rows, ws, rank)
         local_rows = e - b
@@ -87,6 +95,9 @@ class RowShardedAttention:
         piece = (split + self.comm_split - 1) // self.comm_split
         out_dtype = torch.bfloat16 if q.is_cuda else q.dtype
         full = torch.empty((ws, split, H, N, D), dtype=out_dtype, device=q.device)
+        if local_rows < split:
+            full[rank, local_rows:].zero_()        # the padded tail of a ragged split, dropped at the end
+        roots = [dist.get_global_rank(self.group, r) if self.group is not None else r for r in range(ws)]
 
         use_streams = q.is_cuda
         if use_streams and self._comm_stream is None:
@@ -100,30 +111,27 @@ class RowShardedAttention:
                 m = None
                 if mask is not None:
                     m = mask[lo:hi] if mask.dim() >= 2 and mask.shape[0] == local_rows else mask
-                o = self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias)
-                o = pad_to_size(o, p1 - p0, 0)
-            else:  # this rank's block ends before the piece: contribute zero rows
-                o = torch.zeros((p1 - p0, H, N, D), dtype=out_dtype, device=q.device)
-            buf = torch.empty((ws, p1 - p0, H, N, D), dtype=out_dtype, device=q.device)
+                slot = full[rank, lo:hi]
+                if self.writes_in_place:
+                    self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias, out=slot)
+                else:
+                    slot.copy_(self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias))
             if use_streams:
                 ev = torch.cuda.Event()
                 ev.record(torch.cuda.current_stream(q.device))
                 with torch.cuda.stream(self._comm_stream):
                     self._comm_stream.wait_event(ev)
-                    dist.all_gather_into_tensor(buf.view(-1, H, N, D), o, group=self.group)
-                    full[:, p0:p1].copy_(buf)
-                    o.record_stream(self._comm_stream)
-                    buf.record_stream(self._comm_stream)
+                    for r in range(ws):
+                        dist.broadcast(full[r, p0:p1], src=roots[r], group=self.group)
             else:
-                w = dist.all_gather_into_tensor(buf.view(-1, H, N, D), o, group=self.group,
-                                                async_op=True)
-                works.append((w, buf, p0, p1))
-        for w, buf, p0, p1 in works:
+                for r in range(ws):
+                    works.append(dist.broadcast(full[r, p0:p1], src=roots[r], group=self.group, async_op=True))
+        for w in works:
             if not w.wait(timeout=_timedelta(timeout_s)):
-                raise RuntimeError("all_gather did not complete")
-            full[:, p0:p1].copy_(buf)
+                raise RuntimeError("broadcast of an output piece did not complete")
         if use_streams:
             torch.cuda.current_stream(q.device).wait_stream(self._comm_stream)
+            full.record_stream(self._comm_stream)
         record_comm_time("AG Attn", time.time() - t0, full.numel() * full.element_size())
         return full.view(ws * split, H, N, D)[:rows]
 

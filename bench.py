@@ -142,7 +142,7 @@ def _run_port(O, inp, rows):
 
 def rows_for_budget(O, inp, max_rows, target_s):
     """Pair rows whose CPU time is about ``target_s`` seconds (all of them when they fit)."""
-    probe = min(2, max_rows)
+    probe = min(inp["q"].shape[0], max_rows)
     _run_port(O, inp, probe)              # warm: builds / loads the library, touches memory
     t = _run_port(O, inp, probe)
     return int(max(probe, min(max_rows, target_s / max(t, 1e-4) * probe)))
@@ -152,7 +152,7 @@ def time_cpu_port(O, name, shape, target_s):
     """The C restatement of the reference operator on all host threads: one call over as many
     pair rows as fit ``target_s`` seconds."""
     B1, B2, S, D = shape
-    probe_inp = _cpu_inputs(O, name, min(B1, 2))
+    probe_inp = _cpu_inputs(O, name, min(B1, 32))
     rows = rows_for_budget(O, probe_inp, B1, target_s)
     inp = _cpu_inputs(O, name, rows)
     secs = _run_port(O, inp, rows)
@@ -196,7 +196,7 @@ def reference_arm(args, world, rank):
     B1, B2, S, D = c["B1"], c["B2"], c["S"], c["D"]
     n_steps = max(1, args.steps + args.warmup)
     # one step = the whole workload when that costs at most 5 s and the run stays within ~3 minutes
-    probe_inp = _cpu_inputs(O, name, min(B1, 2))
+    probe_inp = _cpu_inputs(O, name, min(B1, 32))
     per_step_s = min(5.0, 180.0 / n_steps)
     rows = rows_for_budget(O, probe_inp, B1, per_step_s)
     inp = _cpu_inputs(O, name, rows)
@@ -356,7 +356,7 @@ def row_sharded_report(args, O, dev, world, rank):
     dist.barrier()
     kernel_ms = max_over_ranks(statistics.median(event_ms(local, 5)))
 
-    fn = lambda q_, k_, v_, m_, b_: dot_product_attention(q_, k_, v_, m_, b_, **kw)
+    fn = lambda q_, k_, v_, m_, b_, out=None: dot_product_attention(q_, k_, v_, m_, b_, out=out, **kw)
     sharder.attention_fn = fn
     gathered = sharder.forward(ql, kl, vl, ml, bias, rows)          # warm-up (NCCL channels, buffers)
     torch.cuda.synchronize()

@@ -385,3 +385,4 @@ def test_debug_dump_shows_the_tensor_core_stages(cuda_device):
     assert (d[3][:, 1] - p_ref.sum(dim=1)).abs().max().item() <= 2e-2 * p_ref.sum(dim=1).max().item()
     ref = O.oracle_fp32(q.cpu(), k.cpu(), v.cpu(), mask, bias.cpu())
     _check_bf16(out.cpu(), ref, "debug build")
+
