@@ -632,7 +632,7 @@ int af3k_qkvg_projection(const void* x, const void* w4, int64_t R, int64_t N, in
   auto enc = tensor_map_encoder();
   if (!enc) return driver_fail("cuTensorMapEncodeTiled entry point", -1);
   const long long M = R * N;
-  if (M > 0x7fffffffLL) return AF3K_ERR_BAD_SHAPE;    // TMA coordinates are 32-bit
+  if (M * kProjC > 0x7fffffffLL) return AF3K_ERR_BAD_SHAPE;    // 32-bit element offsets in the epilogue, 32-bit TMA coordinates
   CUtensorMap tm_x, tm_w;
   {
     cuuint64_t dims[2] = {(cuuint64_t)kProjC, (cuuint64_t)M};

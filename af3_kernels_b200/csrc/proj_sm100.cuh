@@ -196,6 +196,20 @@ qkvg_projection_kernel(const __grid_constant__ ProjParams p, const __grid_consta
       const long long m0 = tile * 128 + quarter * 32;                 // the warp's first row of x
       const long long r0 = m0 / p.N;
       const int tok0 = (int)(m0 - r0 * p.N);
+      // Element offsets of the eight rows this lane stores in every 64-column piece (rows
+      // (lane >> 3) + 4 i), worked out once per tile: into [R, H, N, D] at head 0 and into [M, 128].
+      uint32_t off_qkv[8], off_g[8];
+      uint32_t row_ok = 0;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int row = it * 4 + (lane >> 3);
+        long long r = r0;
+        int tok = tok0 + row;
+        while (tok >= p.N) { tok -= p.N; ++r; }
+        off_qkv[it] = (uint32_t)((r * p.H * p.N + tok) << log2d);
+        off_g[it] = (uint32_t)((m0 + row) * kProjC);
+        if (m0 + row < p.M) row_ok |= 1u << it;
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < 256; c0 += 64) {
         uint32_t acc[64];
@@ -210,40 +224,38 @@ qkvg_projection_kernel(const __grid_constant__ ProjParams p, const __grid_consta
         }
         const int col0 = half * 256 + c0;                             // 64 columns of one output tensor
         const int which = col0 >> 7, within = col0 & 127;             // 0 q, 1 k, 2 v, 3 gate
-        const float mul = which == 0 ? p.q_scale : 1.0f;
+        if (which == 0) {
+#pragma unroll
+          for (int e = 0; e < 64; ++e) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * p.q_scale);
+        }
         // own row -> shared, piece j at position j ^ (row & 7): conflict-free both ways
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const uint32_t w0 = pack_bf16x2(__uint_as_float(acc[8 * j + 0]) * mul, __uint_as_float(acc[8 * j + 1]) * mul);
-          const uint32_t w1 = pack_bf16x2(__uint_as_float(acc[8 * j + 2]) * mul, __uint_as_float(acc[8 * j + 3]) * mul);
-          const uint32_t w2 = pack_bf16x2(__uint_as_float(acc[8 * j + 4]) * mul, __uint_as_float(acc[8 * j + 5]) * mul);
-          const uint32_t w3 = pack_bf16x2(__uint_as_float(acc[8 * j + 6]) * mul, __uint_as_float(acc[8 * j + 7]) * mul);
+          const uint32_t w0 = pack_bf16x2(__uint_as_float(acc[8 * j + 0]), __uint_as_float(acc[8 * j + 1]));
+          const uint32_t w1 = pack_bf16x2(__uint_as_float(acc[8 * j + 2]), __uint_as_float(acc[8 * j + 3]));
+          const uint32_t w2 = pack_bf16x2(__uint_as_float(acc[8 * j + 4]), __uint_as_float(acc[8 * j + 5]));
+          const uint32_t w3 = pack_bf16x2(__uint_as_float(acc[8 * j + 6]), __uint_as_float(acc[8 * j + 7]));
           asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(patch + lane * 128 + ((j ^ (lane & 7)) << 4)),
                        "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
         }
         __syncwarp();
-        // shared -> global: lane l takes piece l & 7 of rows l >> 3, l >> 3 + 4, ...
+        // shared -> global: lane l takes piece l & 7 of rows (l >> 3) + 4 i
+        const int ch = within + 8 * (lane & 7);
+        __nv_bfloat16* dst;
+        if (which == 3) {
+          dst = p.g + ch;
+        } else {
+          const int head = ch >> log2d;
+          dst = (which == 0 ? p.q : (which == 1 ? p.k : p.v)) + (((long long)head * p.N) << log2d) + (ch & (p.D - 1));
+        }
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
-          const int row = it * 4 + (lane >> 3), j = lane & 7;
           uint4 o;
+          const int row = it * 4 + (lane >> 3);
           asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                        : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w)
-                       : "r"(patch + row * 128 + ((j ^ (row & 7)) << 4)));
-          const long long m = m0 + row;
-          if (m < p.M) {
-            const int ch = within + 8 * j;
-            if (which == 3) {
-              *reinterpret_cast<uint4*>(p.g + m * kProjC + ch) = o;
-            } else {
-              long long r = r0;
-              int tok = tok0 + row;
-              while (tok >= p.N) { tok -= p.N; ++r; }
-              __nv_bfloat16* base = which == 0 ? p.q : (which == 1 ? p.k : p.v);
-              const int head = ch >> log2d, d = ch & (p.D - 1);
-              *reinterpret_cast<uint4*>(base + (((r * p.H + head) * p.N + tok) << log2d) + d) = o;
-            }
-          }
+                       : "r"(patch + row * 128 + (((lane & 7) ^ (row & 7)) << 4)));
+          if ((row_ok >> it) & 1u) *reinterpret_cast<uint4*>(dst + (which == 3 ? off_g[it] : off_qkv[it])) = o;
         }
         __syncwarp();      // the patch is rewritten by the next 64 columns
       }
