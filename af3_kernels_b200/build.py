@@ -17,6 +17,7 @@ SOURCES = [os.path.join(CSRC, "af3k_capi.cu")]
 HEADERS = [
     os.path.join(CSRC, "attn_sm100.cuh"),
     os.path.join(CSRC, "pair_bias_sm100.cuh"),
+    os.path.join(CSRC, "proj_sm100.cuh"),
     os.path.join(CSRC, "ptx_sm100.cuh"),
     os.path.join(_HERE, "..", "include", "af3k.h"),
 ]

@@ -185,6 +185,20 @@ __device__ __noinline__ void report_timeout(const Ctx& c, int bar_idx) {
 
 // Warp-collective form: every lane leaves together, so no .sync.aligned instruction is ever
 // executed by part of a warp after a timeout.
+// The same for the single-warp roles, with the waiting loop out of line: these warps run their
+// per-tile loops rarely, next to warps that stream through long unrolled loops, and one pass of
+// such a loop costs 700 - 1 500 cycles whatever it does, so the path taken when nothing has to be
+// waited for is kept short.
+#define AF3K_WAIT_WARP_C(ctx, idx, parity)                                                   \
+  do {                                                                                       \
+    const bool ok_ = mbar_wait_bounded_compact(bar_addr(ctx, idx), (parity), (ctx).p->wait_limit, \
+                                               (ctx).abort_flag);                            \
+    if (!__all_sync(0xffffffffu, ok_)) {                                                     \
+      report_timeout(ctx, idx);                                                              \
+      return;                                                                                \
+    }                                                                                        \
+  } while (0)
+
 #define AF3K_WAIT_WARP(ctx, idx, parity)                                                     \
   do {                                                                                       \
     const bool ok_ = mbar_wait_bounded(bar_addr(ctx, idx), (parity), (ctx).p->wait_limit,    \
@@ -368,7 +382,7 @@ struct QScaler {
       const int r_ = (scaler).step(ctx, lane, false);                                        \
       if (r_ < 0) return;                                                                    \
       if (r_ == 0) {                                                                         \
-        AF3K_WAIT_WARP(ctx, idx, parity);                                                    \
+        AF3K_WAIT_WARP_C(ctx, idx, parity);                                                  \
         break;                                                                               \
       }                                                                                      \
     }                                                                                        \
@@ -396,7 +410,7 @@ __device__ void mask_writer_role(const Ctx& c, int lane) {
           const int nkt = s + 1 < it.gv ? kt : kt + 1;
           if (nkt < p.n_kt) mask_values(p, it, nkt, ns, lane, masked, val);
         }
-        if (round > 0) AF3K_WAIT_WARP(c, BarIdx::kv_empty + st, (round - 1) & 1);
+        if (round > 0) AF3K_WAIT_WARP_C(c, BarIdx::kv_empty + st, (round - 1) & 1);
         const uint32_t slot = c.smem + p.off_mcol + st * kMaskPanelBytes;
 #pragma unroll
         for (int g = 0; g < 4; ++g)
@@ -421,13 +435,15 @@ __device__ void mask_writer_role(const Ctx& c, int lane) {
 // two instruction streams is assumed.
 
 // Logits of every tile, in order: Q K^T, then the mask column, then (bf16 q/k) the bias slices.
-template <bool kTcBias>
+// (The MMA loops are real loops and the fp8 / bf16 choice is a template argument: the warp pays an
+// instruction-cache miss for most lines of this loop on every pass, so the loop is kept small.)
+template <bool kTcBias, bool kFp8>
 __device__ void qk_issuer_role(const Ctx& c) {
   const AttnParams& p = *c.p;
   const bool leader = elect_one();
   const uint32_t nkv = p.kv_stages;
   const uint32_t qk_layout = swizzle_layout_code(p.qk_row_bytes);
-  const bool fp8 = p.qk_is_fp8 != 0;
+  constexpr bool fp8 = kFp8;
   const uint32_t idesc_qk = make_idesc(fp8 ? 0u : 1u, fp8 ? 0u : 1u, 0u, 0u, kTile);
   const uint32_t kv_stage_bytes = p.k_tile_bytes + p.v_tile_bytes;
   // descriptor words for tile 0 / stage 0; later tiles only move the start-address field
@@ -465,19 +481,27 @@ __device__ void qk_issuer_role(const Ctx& c) {
     const int gv = it.gv;
     for (int kt = 0; kt < p.n_kt; ++kt) {
       for (int s = 0; s < gv; ++s) {
-        if (kTcBias && (s == 0 || p.q_split)) AF3K_WAIT_WARP(c, BarIdx::bias_full + bst, b_par);
         const int b = s & 1;
-        // the softmax warpgroup of this buffer must have read the previous logits tile
-        if (b) {
-          if (!first[1]) { AF3K_WAIT_WARP(c, BarIdx::s_free + 1, sfree_par[1]); sfree_par[1] ^= 1; }
-          first[1] = 0;
-        } else {
-          if (!first[0]) { AF3K_WAIT_WARP(c, BarIdx::s_free + 0, sfree_par[0]); sfree_par[0] ^= 1; }
-          first[0] = 0;
-        }
         const int qslot = (int)q_buf(p, icount) * kMaxStreams + s;
-        if (kt == 0) AF3K_WAIT_WARP(c, (p.scale_q ? BarIdx::q_scaled : BarIdx::q_full) + qslot, q_use(p, icount) & 1);
-        AF3K_WAIT_WARP(c, BarIdx::kv_full + st, kv_par);
+        const int q_bar = (p.scale_q ? BarIdx::q_scaled : BarIdx::q_full) + qslot;
+        const bool need_bias = kTcBias && (s == 0 || p.q_split);
+        const bool need_sfree = !first[b];
+        {
+          // everything the tile needs is normally there already: test all its barriers, vote once
+          bool ok = mbar_test_wait(bar_addr(c, BarIdx::kv_full + st), kv_par);
+          if (need_sfree) ok = mbar_test_wait(bar_addr(c, BarIdx::s_free + b), sfree_par[b]) && ok;
+          if (need_bias) ok = mbar_test_wait(bar_addr(c, BarIdx::bias_full + bst), b_par) && ok;
+          if (kt == 0) ok = mbar_test_wait(bar_addr(c, q_bar), q_use(p, icount) & 1) && ok;
+          if (!__all_sync(0xffffffffu, ok)) {
+            if (need_bias) AF3K_WAIT_WARP_C(c, BarIdx::bias_full + bst, b_par);
+            // the softmax warpgroup of this buffer must have read the previous logits tile
+            if (need_sfree) AF3K_WAIT_WARP_C(c, BarIdx::s_free + b, sfree_par[b]);
+            if (kt == 0) AF3K_WAIT_WARP_C(c, q_bar, q_use(p, icount) & 1);
+            AF3K_WAIT_WARP_C(c, BarIdx::kv_full + st, kv_par);
+          }
+        }
+        if (need_sfree) sfree_par[b] ^= 1;
+        first[b] = 0;
         tc_fence_after();
         const uint32_t a_lo = qd_lo + (q_buf(p, icount) * p.n_streams + s) * q_step;
         const uint32_t b_lo = kd_lo + st * stage_step;
@@ -486,19 +510,17 @@ __device__ void qk_issuer_role(const Ctx& c) {
         const uint32_t bias_lo = bd_lo + bst * (kBiasTileBytes >> 4);
         if (leader) {
           const long long t0 = tl != nullptr ? clock64() : 0;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {     // one K step = 32 bytes of a tile row
-            if (k < ksteps) {
-              if (fp8) mma_ss_f8(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
-              else     mma_ss_f16(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
-            }
+#pragma unroll 1
+          for (int k = 0; k < ksteps; ++k) {     // one K step = 32 bytes of a tile row
+            if (fp8) mma_ss_f8(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
+            else     mma_ss_f16(s_tmem, a_lo + 2 * k, qd_hi, b_lo + 2 * k, kd_hi, idesc_qk, k > 0 ? 1u : 0u);
           }
           // mask column: start address and leading offset both move with the ring slot (the
           // zero block stays put)
           if (mask_col)
             mma_ss_f16(s_tmem, od_lo, od_hi, md_lo + slot16 - (slot16 << 16), md_hi, idesc_mask, 1u);
           if (kTcBias) {
-#pragma unroll
+#pragma unroll 1
             for (int k = 0; k < kTile / 16; ++k)   // keys 16k .. 16k + 15: box k / 4, 32 bytes per step
               mma_ss_f16(s_tmem + 16 * k, bias_lo + (k >> 2) * (kBiasTileBytes >> 5) + 2 * (k & 3), bd_hi,
                          id_lo, id_hi, idesc_bias, 1u);
@@ -560,7 +582,7 @@ __device__ void pv_issuer_role(const Ctx& c, int lane) {
         else   { AF3K_WAIT_WARP_OR_SCALE(c, BarIdx::p_ready + 0, pready_par[0], scaler, lane); pready_par[0] ^= 1; }
         // the warpgroup's epilogue of the previous item must have read its O accumulators before
         // its first P V of this item overwrites one
-        if (kt == 0 && s < 2 && icount > 0) AF3K_WAIT_WARP(c, BarIdx::epi_done + b, (icount - 1) & 1);
+        if (kt == 0 && s < 2 && icount > 0) AF3K_WAIT_WARP_C(c, BarIdx::epi_done + b, (icount - 1) & 1);
         tc_fence_after();
         const uint32_t b_lo = vd_lo + st * stage_step;
         const uint32_t o_tmem = c.tmem + kOCol + s * p.nv;
@@ -568,7 +590,7 @@ __device__ void pv_issuer_role(const Ctx& c, int lane) {
         if (leader) {
           const long long t0 = tl != nullptr ? clock64() : 0;
           mma_ts_f16(o_tmem, p_tmem, b_lo, vd_hi, idesc_pv, kt > 0 ? 1u : 0u);
-#pragma unroll
+#pragma unroll 1
           for (int k = 1; k < kTile / 16; ++k)   // 16 keys per step: 8 TMEM columns of P
             mma_ts_f16(o_tmem, p_tmem + k * 8, b_lo + k * v_kstep, vd_hi, idesc_pv, 1u);
           // one completion signal: the K/V stage is free, and so are this tile's P buffer and O
@@ -971,7 +993,8 @@ attention_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ C
     if (warp == 0) {
       if (lane == 0) producer_role(c, &tm_q, &tm_k, &tm_v, &tm_bias);
     } else if (warp == 1) {
-      qk_issuer_role<kTcBias>(c);
+      if (p.qk_is_fp8) qk_issuer_role<kTcBias, true>(c);
+      else             qk_issuer_role<kTcBias, false>(c);
     } else if (warp == 2) {
       pv_issuer_role<kTcBias>(c, lane);
     } else if (warp == 3) {

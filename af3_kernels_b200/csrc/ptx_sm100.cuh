@@ -93,6 +93,29 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     }
   }
 }
+// The same with the waiting loop out of line, for the single-warp roles: they run their per-tile
+// loops rarely, next to warps that stream through long unrolled loops, and pay an instruction-cache
+// miss for most lines they touch, so the code they run when nothing has to be waited for is kept
+// short.  (The softmax warps keep the inline form: a call would have to save their registers.)
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, long long limit_cycles,
+                                            volatile int* abort_flag) {
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_park(bar, parity, 2000u)) return true;
+    if ((++spins & 15u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - t0 > limit_cycles) return false;
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait_bounded_compact(uint32_t bar, uint32_t parity,
+                                                          long long limit_cycles,
+                                                          volatile int* abort_flag) {
+  if (mbar_test_wait(bar, parity)) return true;
+  if (mbar_try_wait_park(bar, parity, 2000u)) return true;    // most real waits end inside one parked attempt
+  return mbar_wait_slow(bar, parity, limit_cycles, abort_flag);
+}
 
 // One lane of a converged warp (the same lane every time it is asked within a kernel run).
 __device__ __forceinline__ bool elect_one() {
