@@ -58,7 +58,7 @@ class AttentionDesc(ctypes.Structure):
         ("softmax_scale", ctypes.c_float),
         ("rows_per_item", ctypes.c_int32),
         ("bias_prescaled", ctypes.c_int32),
-        ("reserved_", ctypes.c_int32),
+        ("max_ctas", ctypes.c_int32),
     ]
 
 

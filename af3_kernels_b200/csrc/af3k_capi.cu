@@ -138,7 +138,7 @@ int validate(const af3k_attention_desc& d) {
   if (d.rows_per_item < 0 || d.rows_per_item > 8) return AF3K_ERR_BAD_SHAPE;   // a request, clamped by the plan
   if (d.bias_prescaled != 0 && (d.bias_prescaled != 1 || d.qk_dtype != AF3K_FP8_E4M3 || d.bias_dtype != AF3K_BF16))
     return AF3K_ERR_BAD_DTYPE;
-  if (d.reserved_ != 0) return AF3K_ERR_BAD_SHAPE;
+  if (d.max_ctas < 0) return AF3K_ERR_BAD_SHAPE;
   const int64_t es = d.qk_dtype == AF3K_FP8_E4M3 ? 1 : 2;
   for (int i = 0; i < 3; ++i) {
     if (d.q_stride[i] < 0 || d.k_stride[i] < 0 || d.v_stride[i] < 0 || d.out_stride[i] < 0)
@@ -213,7 +213,8 @@ int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan, b
       if (stages < 2) continue;
       const long long groups = (p.B1 + g - 1) / g;
       const long long items = groups * p.B2 * (split ? (p.n_qt + 1) / 2 : p.n_qt);
-      const long long rounds = (items + dev.sm_count - 1) / dev.sm_count;
+      const int ctas_avail = (d.max_ctas > 0 && d.max_ctas < dev.sm_count) ? d.max_ctas : dev.sm_count;
+      const long long rounds = (items + ctas_avail - 1) / ctas_avail;
       // streams alternate between the two softmax warpgroups: an odd count leaves one idle slot.
       // A CTA's time, in logits-tile times of one warpgroup: per item n_kt tiles for each of its
       // slots / 2 streams plus about 0.8 for the epilogue and the hand-over to the next item; with
@@ -254,7 +255,8 @@ int make_plan(const af3k_attention_desc& d, const DeviceInfo& dev, Plan* plan, b
   // shared memory even when the tiles need less.
   if (smem < 120 * 1024) smem = 120 * 1024;
   plan->smem_bytes = smem;
-  plan->grid = p.n_items < dev.sm_count ? p.n_items : dev.sm_count;
+  const int ctas = (d.max_ctas > 0 && d.max_ctas < dev.sm_count) ? d.max_ctas : dev.sm_count;
+  plan->grid = p.n_items < ctas ? p.n_items : ctas;
   return AF3K_OK;
 }
 
@@ -344,7 +346,7 @@ int static_scratch_address(void** out) {
 
 extern "C" {
 
-int af3k_version(void) { return 1001; }
+int af3k_version(void) { return 1002; }
 
 const char* af3k_strerror(int code) {
   switch (code) {

@@ -37,11 +37,21 @@ class RowShardedAttention:
     CPU ranks (gloo) pass a stand-in so that the partition / gather logic is exercised without a GPU.
     """
 
-    def __init__(self, group=None, comm_split: int = 4, attention_fn: Optional[Callable] = None):
+    def __init__(self, group=None, comm_split: int = 8, attention_fn: Optional[Callable] = None,
+                 comm_sms: int = 8):
         if comm_split < 1:
             raise ValueError("comm_split must be >= 1")
         self.group = group
         self.comm_split = comm_split
+        # The attention kernel is persistent, one CTA per SM, each taking the SM's whole shared
+        # memory and TMEM: a collective launched beside it finds no SM until it ends, and the
+        # gather of piece i then runs after kernel i + 1 instead of under it.  So the kernels of a
+        # gathered forward leave `comm_sms` SMs free (0 = use all).  Measured on two GPUs (2 048 rows of
+        # N = 2 048, fp8 q/k): 7.17 ms with every SM and four pieces, 6.97 ms with eight SMs left free
+        # and eight pieces; capping NCCL's own CTAs (NCCL_MAX_CTAS) only made the transfers slower.
+        self.comm_sms = comm_sms
+        # how the pieces travel on CUDA ranks: "sendrecv" (grouped point-to-point) or "broadcast"
+        self.exchange = "sendrecv"
         # the CUDA operator writes into a caller-provided ``out``; a stand-in (CPU tests) returns its result
         self.writes_in_place = attention_fn is None
         if attention_fn is None:
@@ -113,7 +123,11 @@ class RowShardedAttention:
                     m = mask[lo:hi] if mask.dim() >= 2 and mask.shape[0] == local_rows else mask
                 slot = full[rank, lo:hi]
                 if self.writes_in_place:
-                    self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias, out=slot)
+                    kw = {}
+                    if q.is_cuda and ws > 1 and self.comm_sms > 0:
+                        sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+                        kw["max_ctas"] = max(1, sms - self.comm_sms)
+                    self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias, out=slot, **kw)
                 else:
                     slot.copy_(self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias))
             if use_streams:
@@ -121,8 +135,20 @@ class RowShardedAttention:
                 ev.record(torch.cuda.current_stream(q.device))
                 with torch.cuda.stream(self._comm_stream):
                     self._comm_stream.wait_event(ev)
-                    for r in range(ws):
-                        dist.broadcast(full[r, p0:p1], src=roots[r], group=self.group)
+                    if self.exchange == "sendrecv":
+                        # one grouped launch per piece: this rank's slot goes to every peer while
+                        # theirs arrive, both directions of every link busy at once
+                        ops = []
+                        for r in range(ws):
+                            if r != rank:
+                                ops.append(dist.P2POp(dist.isend, full[rank, p0:p1], roots[r], group=self.group))
+                                ops.append(dist.P2POp(dist.irecv, full[r, p0:p1], roots[r], group=self.group))
+                        if ops:
+                            for w in dist.batch_isend_irecv(ops):
+                                w.wait()       # orders the comm stream behind the transfer; the host does not block
+                    else:
+                        for r in range(ws):
+                            dist.broadcast(full[r, p0:p1], src=roots[r], group=self.group)
             else:
                 for r in range(ws):
                     works.append(dist.broadcast(full[r, p0:p1], src=roots[r], group=self.group, async_op=True))

@@ -152,6 +152,7 @@ def dot_product_attention(
     check_status: Optional[bool] = None,
     use_workspace: bool = True,
     cache_bias: bool = True,
+    max_ctas: int = 0,
 ) -> torch.Tensor:
     """softmax(scale * q k^T + bias, key-masked) v on the current CUDA stream.
 
@@ -163,6 +164,7 @@ def dot_product_attention(
     softmax threads add the bias themselves.  ``bias`` may be a ``StagedBias``; a plain tensor
     that needs the staging pass is staged once and the copy is reused while the same, unmodified
     tensor object keeps being passed (``cache_bias=False`` stages inside every call instead).
+    ``max_ctas`` > 0 caps the kernel's grid, leaving the other SMs to a kernel that runs beside it.
     """
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
         raise ValueError("q, k, v must be 4-D [B1, B2, S, D]")
@@ -192,6 +194,7 @@ def dot_product_attention(
             return dot_product_attention(
                 q.to(torch.bfloat16), k, v, mask, bias, softmax_scale=softmax_scale,
                 rows_per_item=rows_per_item, check_status=check_status, use_workspace=use_workspace,
+                max_ctas=max_ctas,
             ).to(torch.float32)
         if q.dtype != torch.bfloat16:
             raise TypeError(f"q must be bfloat16, float32 or float8_e4m3fn, got {q.dtype}")
@@ -254,6 +257,7 @@ def dot_product_attention(
     desc.softmax_scale = scale
     desc.rows_per_item = int(rows_per_item)
     desc.bias_prescaled = 1 if prescaled else 0
+    desc.max_ctas = int(max_ctas)
 
     lib = _capi.load()
     with torch.cuda.device(q.device):

@@ -329,7 +329,7 @@ def row_sharded_report(args, O, dev, world, rank):
         dist.all_reduce(v, op=dist.ReduceOp.MAX)
         return v.item()
 
-    sharder = RowShardedAttention(comm_split=4)
+    sharder = RowShardedAttention(comm_split=8)
     # replicated operands: one NCCL broadcast each into every GPU's own memory (first one warms NCCL up)
     sharder.broadcast_shared(bias.clone(), mask_u8.clone())
     torch.cuda.synchronize()
@@ -356,7 +356,7 @@ def row_sharded_report(args, O, dev, world, rank):
     dist.barrier()
     kernel_ms = max_over_ranks(statistics.median(event_ms(local, 5)))
 
-    fn = lambda q_, k_, v_, m_, b_, out=None: dot_product_attention(q_, k_, v_, m_, b_, out=out, **kw)
+    fn = lambda q_, k_, v_, m_, b_, out=None, max_ctas=0: dot_product_attention(q_, k_, v_, m_, b_, out=out, max_ctas=max_ctas, **kw)
     sharder.attention_fn = fn
     gathered = sharder.forward(ql, kl, vl, ml, bias, rows)          # warm-up (NCCL channels, buffers)
     torch.cuda.synchronize()
@@ -364,12 +364,18 @@ def row_sharded_report(args, O, dev, world, rank):
     eq = torch.tensor([1 if equal else 0], dtype=torch.int32, device=dev)
     dist.all_reduce(eq, op=dist.ReduceOp.MIN)
     del gathered
-    times = []
-    for _ in range(3):
-        dist.barrier()
-        torch.cuda.synchronize()
-        times.append(event_ms(lambda: sharder.forward(ql, kl, vl, ml, bias, rows), 1)[0])
-    total_ms = max_over_ranks(statistics.median(times))
+    def timed_forward():
+        times = []
+        for _ in range(3):
+            dist.barrier()
+            torch.cuda.synchronize()
+            times.append(event_ms(lambda: sharder.forward(ql, kl, vl, ml, bias, rows), 1)[0])
+        return max_over_ranks(statistics.median(times))
+    total_ms = timed_forward()
+    comm_sms = sharder.comm_sms
+    sharder.comm_sms = 0          # for comparison: the kernel on every SM, the collective finds none free
+    total_ms_all_sms = timed_forward()
+    sharder.comm_sms = comm_sms
 
     out_bytes = rows * B2 * S * D * 2
     inbound = out_bytes * (world - 1) / world
@@ -386,9 +392,12 @@ def row_sharded_report(args, O, dev, world, rank):
         "gather_inbound_bytes_per_gpu": inbound, "gather_floor_ms": floor_ms,
         "gather_floor_basis": f"{NVLINK_GBS_PER_DIRECTION:.0f} GB/s per direction per GPU (nominal NVLink 5)",
         "gather_floor_ms_at_770_gbs": inbound / 770e9 * 1e3,
-        "comm_split": sharder.comm_split, "sharded_equals_single": bool(eq.item() == 1),
+        "comm_split": sharder.comm_split, "comm_sms": comm_sms, "exchange": sharder.exchange,
+        "total_ms_kernel_on_all_sms": total_ms_all_sms, "E2_kernel_on_all_sms": t1_ms / (world * total_ms_all_sms),
+        "sharded_equals_single": bool(eq.item() == 1),
         "definitions": "E1 = t1 / (N * slowest rank's kernel on its row block); E2 = t1 / (N * time of "
-                       "RowShardedAttention.forward: kernel pieces + chunked NCCL all-gather on a side stream)",
+                       "RowShardedAttention.forward: kernel pieces that leave comm_sms SMs free + the pieces' "
+                       "in-place exchange (NCCL grouped send/recv) on a side stream)",
     }
 
 

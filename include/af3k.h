@@ -64,7 +64,9 @@ typedef struct af3k_attention_desc {
   int32_t rows_per_item;  /* 0 = choose; else requested pair rows per staged bias tile (1..8, clamped to what fits, at most 4) */
   int32_t bias_prescaled; /* fp8 q/k only: 1 = `bias` is the output of af3k_stage_bias for these scales (already divided
                              by the head's logit scale); the tensor core adds it and no staging pass runs.  0 otherwise. */
-  int32_t reserved_;      /* must be 0 */
+  int32_t max_ctas;       /* 0 = one CTA per SM; > 0: at most this many CTAs, leaving the other SMs to
+                             kernels that run beside this one (the collective that gathers a
+                             row-sharded output while the next piece is computed) */
 } af3k_attention_desc;
 
 /* Library / ABI version (major * 1000 + minor). */

@@ -70,6 +70,17 @@ def test_launch_plan_fits_b200(shape):
     assert plan["items"] == groups * B2 * n_qt
 
 
+def test_max_ctas_caps_the_grid():
+    d = _desc(768, 4, 768, 32)
+    full = _capi.describe_plan(d)
+    d.max_ctas = 140
+    capped = _capi.describe_plan(d)
+    assert capped["grid"] == min(140, full["grid"]) and capped["items"] == full["items"]
+    d.max_ctas = -1
+    out = (ctypes.c_int32 * 6)()
+    assert _capi.load().af3k_describe_plan(ctypes.byref(d), out) == 2
+
+
 def test_argument_validation_codes():
     lib = _capi.load()
     out = (ctypes.c_int32 * 6)()
