@@ -50,7 +50,8 @@ class RowShardedAttention:
         # N = 2 048, fp8 q/k): 7.17 ms with every SM and four pieces, 6.97 ms with eight SMs left free
         # and eight pieces; capping NCCL's own CTAs (NCCL_MAX_CTAS) only made the transfers slower.
         self.comm_sms = comm_sms
-        # how the pieces travel on CUDA ranks: "sendrecv" (grouped point-to-point) or "broadcast"
+        # how the pieces travel on CUDA ranks: "sendrecv" (grouped point-to-point, in place), "broadcast"
+        # (one per rank, in place) or "allgather" (one collective into a staging buffer + a copy)
         self.exchange = "sendrecv"
         # the CUDA operator writes into a caller-provided ``out``; a stand-in (CPU tests) returns its result
         self.writes_in_place = attention_fn is None
@@ -146,6 +147,12 @@ class RowShardedAttention:
                         if ops:
                             for w in dist.batch_isend_irecv(ops):
                                 w.wait()       # orders the comm stream behind the transfer; the host does not block
+                    elif self.exchange == "allgather":
+                        # one collective per piece into a staging buffer, then one strided copy into place
+                        tmp = torch.empty((ws, p1 - p0, H, N, D), dtype=out_dtype, device=q.device)
+                        dist.all_gather_into_tensor(tmp, full[rank, p0:p1].contiguous(), group=self.group)
+                        full[:, p0:p1].copy_(tmp)
+                        tmp.record_stream(self._comm_stream)
                     else:
                         for r in range(ws):
                             dist.broadcast(full[r, p0:p1], src=roots[r], group=self.group)

@@ -236,6 +236,21 @@ def test_rows_per_item_choices_give_identical_bits(cuda_device):
         assert torch.equal(_run(cuda_device, q, k, v, mask, bias, rows_per_item=G), base), G
 
 
+def test_capped_grid_gives_identical_bits(cuda_device):
+    """max_ctas (SMs left to a collective running beside the kernel) changes which CTA takes which
+    work item, nothing else."""
+    g = torch.Generator().manual_seed(15)
+    B1, B2, S, D = 40, 4, 300, 32
+    q = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B1, B2, S, D, generator=g).to(torch.bfloat16)
+    bias = torch.randn(B2, S, S, generator=g).to(torch.bfloat16)
+    mask = torch.rand(B1, S, generator=g) >= 0.05
+    base = _run(cuda_device, q, k, v, mask, bias)
+    for cap in (1, 7, 100, 140, 1000):
+        assert torch.equal(_run(cuda_device, q, k, v, mask, bias, max_ctas=cap), base), cap
+
+
 def test_strided_inputs_and_output(cuda_device):
     dev = cuda_device
     g = torch.Generator().manual_seed(6)
