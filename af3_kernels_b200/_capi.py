@@ -30,6 +30,7 @@ EXPORTED_SYMBOLS = (
     "af3k_last_launch_count",
     "af3k_set_wait_limit_cycles",
     "af3k_describe_plan",
+    "af3k_pair_bias_status",
     "af3k_debug_set_dump",
     "af3k_selftest_wait_timeout",
     "af3k_pair_bias",
@@ -113,6 +114,8 @@ def load() -> ctypes.CDLL:
     lib.af3k_pair_bias.restype = ctypes.c_int
     lib.af3k_pair_bias.argtypes = [vp, ctypes.c_int32, i64, i64, i64, i64, vp, vp, vp, ctypes.c_float, vp, vp,
                                    i64, vp]
+    lib.af3k_pair_bias_status.restype = ctypes.c_int
+    lib.af3k_pair_bias_status.argtypes = [ctypes.POINTER(ctypes.c_int32)]
     lib.af3k_qkvg_projection.restype = ctypes.c_int
     lib.af3k_qkvg_projection.argtypes = [vp, vp, i64, i64, i64, ctypes.c_float, vp, vp, vp, vp, vp, vp]
     lib.af3k_sigmoid_gate.restype = ctypes.c_int

@@ -102,6 +102,8 @@ int device_info(DeviceInfo** out) {
         (e = cudaFuncSetAttribute(pair_bias_kernel_t<__nv_bfloat16>, attr, PbTile<__nv_bfloat16>::kSmemBytes)) !=
             cudaSuccess)
       return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize, pair_bias)", e);
+    if ((e = cudaFuncSetAttribute(pair_bias_mma_kernel, attr, kPbmSmemBytes)) != cudaSuccess)
+      return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize, pair_bias_mma)", e);
     if ((e = cudaFuncSetAttribute(qkvg_projection_kernel, attr, (int)kProjSmemBytes)) != cudaSuccess)
       return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize, qkvg_projection)", e);
     d.attr_set = true;
@@ -598,7 +600,16 @@ int af3k_pair_bias(const void* pair, int32_t pair_dtype, int64_t R, int64_t N, i
   const unsigned grid = (unsigned)(n_tiles < max_ctas ? n_tiles : max_ctas);
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
   const bool f32 = pair_dtype == AF3K_F32;
-  if (H <= 4) {
+#ifndef AF3K_PB_MMA_MIN_HEADS
+#define AF3K_PB_MMA_MIN_HEADS 5
+#endif
+  if (!f32 && H >= AF3K_PB_MMA_MIN_HEADS) {
+    // bf16 pair, more than four heads: moments and normalisation per thread, the head projection on
+    // the tensor core (its time does not depend on the head count)
+    const long long cap = (long long)dev->sm_count * 5;
+    const unsigned grid_m = (unsigned)(n_tiles < cap ? n_tiles : cap);
+    pair_bias_mma_kernel<<<grid_m, kPbmRows, kPbmSmemBytes, stream>>>(p, wait_limit_cycles());
+  } else if (H <= 4) {
     // one thread per vector, tiles transposed through shared memory; five CTAs fit an SM
     const long long tiles_t = R * ((N + (f32 ? 64 : 128) - 1) / (f32 ? 64 : 128));
     const long long cap = (long long)dev->sm_count * 5;
@@ -616,6 +627,20 @@ int af3k_pair_bias(const void* pair, int32_t pair_dtype, int64_t R, int64_t N, i
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("launch pair_bias_kernel", e);
   t_last_launches = 1;
+  return AF3K_OK;
+}
+
+int af3k_pair_bias_status(int32_t* out4) {
+  if (out4 == nullptr) return AF3K_ERR_NULL_POINTER;
+  int host[4] = {0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyFromSymbol(host, g_pair_bias_status, sizeof(host));
+  if (e != cudaSuccess) return cuda_fail("cudaMemcpyFromSymbol(pair-bias status)", e);
+  for (int i = 0; i < 4; ++i) out4[i] = host[i];
+  if (host[0] != 0) {
+    const int zero[4] = {0, 0, 0, 0};
+    if ((e = cudaMemcpyToSymbol(g_pair_bias_status, zero, sizeof(zero))) != cudaSuccess)
+      return cuda_fail("cudaMemcpyToSymbol(pair-bias status)", e);
+  }
   return AF3K_OK;
 }
 

@@ -332,6 +332,228 @@ __global__ void __launch_bounds__(PbTile<T>::kRows, 640 / PbTile<T>::kRows) pair
   }
 }
 
+// ---------------------------------------------------------------- bf16 pair, up to 16 heads: projection on the tensor core
+// The thread-per-vector kernel above is bound by instruction issue, and a third of its
+// instructions are the head projection (per channel and head one FMA and a share of a
+// shared-memory read, on values unpacked again from their bf16 rounding).  That projection is a
+// small GEMM, [128 vectors, 128 channels] x [128 channels, 16 heads], so here the tensor core does
+// it: the tile sits in shared memory in the layout a tcgen05.mma A operand wants (K-major rows
+// of 128 bytes, 128-byte swizzle, the two 64-channel halves 16 KB apart), thread t still walks
+// over row t twice (moments; normalise and round, written back in place), one thread then issues
+// eight MMAs (M 128, N 32, K 16) against the projection weights - each fp32 weight as a bf16 high
+// part (B rows 0-15) plus a bf16 low part (rows 16-31), so that fp32 weights are not rounded to
+// bf16 -, and while they run all threads copy the normalised tile out.  The accumulator (32 fp32
+// columns of TMEM, lane = vector) comes back with one tcgen05.ld per thread; head h is column h
+// plus column 16 + h.  The swizzle also keeps both the per-thread row walks
+// and the coalesced copies free of bank conflicts, like the padding of the kernel above.
+constexpr int kPbmRows = 128;                       // vectors per tile = threads per CTA
+constexpr int kPbmHalfBytes = kPbmRows * 128;       // one 64-channel half of the tile
+constexpr uint32_t kPbmTmemCols = 32;
+// dynamic shared memory from a 1024-aligned base: tile, weights (same layout, 16 rows), gamma / beta,
+// bias staging [16][128] bf16, mbarrier + TMEM address slot
+constexpr int kPbmOffW = 2 * kPbmHalfBytes;
+constexpr int kPbmWRows = 32;                       // B operand rows: 16 heads x {high, low} part
+constexpr int kPbmOffC = kPbmOffW + 2 * kPbmWRows * 128;
+constexpr int kPbmOffBias = kPbmOffC + 2 * kPbChannels * 4;
+constexpr int kPbmOffBar = kPbmOffBias + kPbMaxHeads * kPbmRows * 2;
+constexpr int kPbmSmemBytes = kPbmOffBar + 16 + 1024;
+
+__device__ int g_pair_bias_status[4];   // {1 = a bounded wait ran out, block, tile (low word), 0}
+
+__device__ __forceinline__ uint32_t pbm_swz(int row, int piece) {   // byte offset of 16-byte piece 0..15 of a row
+  return (uint32_t)((piece >> 3) * kPbmHalfBytes + row * 128 + (((piece & 7) ^ (row & 7)) << 4));
+}
+
+__global__ void __launch_bounds__(kPbmRows, 5) pair_bias_mma_kernel(const PairBiasParams p, long long wait_limit) {
+  extern __shared__ uint8_t pbm_raw[];
+  const uint32_t base = (smem_u32(pbm_raw) + 1023u) & ~1023u;
+  uint8_t* gbase = pbm_raw + (base - smem_u32(pbm_raw));
+  float* s_c = reinterpret_cast<float*>(gbase + kPbmOffC);                       // gamma, beta
+  __nv_bfloat16* s_bias = reinterpret_cast<__nv_bfloat16*>(gbase + kPbmOffBias);  // [16][128]
+  const uint32_t bar = base + kPbmOffBar;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + kPbmOffBar + 8);
+  __shared__ int abort_flag;
+  const int t = threadIdx.x, warp = t >> 5;
+
+  if (t == 0) {
+    abort_flag = 0;
+    mbar_init(bar, 1);
+    fence_barrier_init();
+  }
+  s_c[t] = p.gamma[t];
+  s_c[kPbChannels + t] = p.beta[t];
+  // projection weights as the B operand: row = head (+ 16 for the low parts; absent heads zero), K = channel
+  for (int k = t; k < kPbmWRows * 16; k += kPbmRows) {
+    const int r = k >> 4, piece = k & 15, h = r & 15;
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+    if (h < p.H) {
+      const float* src = p.proj + h * kPbChannels + piece * 8;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float a = src[2 * e], b = src[2 * e + 1];
+        if (r >= 16) {   // what the bf16 high part leaves over
+          a -= __bfloat162float(__float2bfloat16_rn(a));
+          b -= __bfloat162float(__float2bfloat16_rn(b));
+        }
+        w[e] = pb_pack_bf16x2(a, b);
+      }
+    }
+    const uint32_t off = (uint32_t)((piece >> 3) * (kPbmWRows * 128) + r * 128 + (((piece & 7) ^ (r & 7)) << 4));
+    *reinterpret_cast<uint4*>(gbase + kPbmOffW + off) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  fence_proxy_async_smem();
+  if (warp == 0) {
+    tmem_alloc(base + kPbmOffBar + 8, kPbmTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t idesc = make_idesc(1u, 1u, 0u, 0u, kPbmWRows);
+  const uint64_t adesc = make_smem_desc(base, 16, 8 * 128, 2);
+  const uint64_t bdesc = make_smem_desc(base + kPbmOffW, 16, 8 * 128, 2);
+
+  const int tiles_j = (p.N + kPbmRows - 1) / kPbmRows;
+  const long long n_tiles = (long long)p.R * tiles_j;
+  uint32_t phase = 0;
+  bool ok = true;
+  for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    const int i = (int)(tile / tiles_j);
+    const int j0 = (int)(tile % tiles_j) * kPbmRows;
+    const int rows = min(kPbmRows, p.N - j0);
+    const long long vec0 = (long long)i * p.N + j0;
+    // global -> shared, coalesced, as asynchronous 16-byte copies into the swizzled positions
+    {
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.pair) + vec0 * kPbChannels);
+      for (int k = t; k < rows * 16; k += kPbmRows)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(base + pbm_swz(k >> 4, k & 15)), "l"(src + k) : "memory");
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    {
+      // rows beyond the sequence are normalised too (whatever the buffer holds; finite after the
+      // clamp below) so that the MMA reads defined values; they are never stored
+      const bool live = t < rows;
+      float pivot;
+      {
+        float x[8];
+        pb_unpack8<__nv_bfloat16>(*reinterpret_cast<const uint4*>(gbase + pbm_swz(t, 0)), make_uint4(0, 0, 0, 0), x);
+        pivot = live ? x[0] : 0.f;
+      }
+      const uint64_t npivot2 = pack_f32x2(-pivot, -pivot);
+      uint64_t s1a = pack_f32x2(0.f, 0.f), s1b = s1a, s2a = s1a, s2b = s1a;
+#pragma unroll 4
+      for (int c8 = 0; c8 < 16; ++c8) {
+        float x[8];
+        pb_unpack8<__nv_bfloat16>(*reinterpret_cast<const uint4*>(gbase + pbm_swz(t, c8)), make_uint4(0, 0, 0, 0), x);
+#pragma unroll
+        for (int e = 0; e < 8; e += 4) {
+          const uint64_t da = add_f32x2(pack_f32x2(x[e], x[e + 1]), npivot2);
+          const uint64_t db = add_f32x2(pack_f32x2(x[e + 2], x[e + 3]), npivot2);
+          s1a = add_f32x2(s1a, da); s1b = add_f32x2(s1b, db);
+          s2a = fma_f32x2(da, da, s2a); s2b = fma_f32x2(db, db, s2b);
+        }
+      }
+      float s1lo, s1hi, s2lo, s2hi;
+      unpack_f32x2(add_f32x2(s1a, s1b), s1lo, s1hi);
+      unpack_f32x2(add_f32x2(s2a, s2b), s2lo, s2hi);
+      const float m1 = (s1lo + s1hi) * (1.0f / kPbChannels);
+      const float mean = live ? pivot + m1 : 0.f;
+      const float var = fmaxf((s2lo + s2hi) * (1.0f / kPbChannels) - m1 * m1, 0.f);
+      const float rstd = live ? rsqrtf(var + p.eps) : 0.f;
+      // z = (x - mean) * rstd as one FMA, y = z * gamma + beta as another
+      const uint64_t rstd2 = pack_f32x2(rstd, rstd);
+      const float nmr = -mean * rstd;
+      const uint64_t nmr2 = pack_f32x2(nmr, nmr);
+#pragma unroll 4
+      for (int c8 = 0; c8 < 16; ++c8) {
+        const uint32_t off = pbm_swz(t, c8);
+        float x[8];
+        pb_unpack8<__nv_bfloat16>(*reinterpret_cast<const uint4*>(gbase + off), make_uint4(0, 0, 0, 0), x);
+        uint32_t yw[4];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const ulonglong2 g4 = *reinterpret_cast<const ulonglong2*>(&s_c[c8 * 8 + 4 * q]);
+          const ulonglong2 b4 = *reinterpret_cast<const ulonglong2*>(&s_c[kPbChannels + c8 * 8 + 4 * q]);
+          const uint64_t z01 = fma_f32x2(pack_f32x2(x[4 * q], x[4 * q + 1]), rstd2, nmr2);
+          const uint64_t z23 = fma_f32x2(pack_f32x2(x[4 * q + 2], x[4 * q + 3]), rstd2, nmr2);
+          float y0, y1, y2, y3;
+          unpack_f32x2(fma_f32x2(z01, g4.x, b4.x), y0, y1);
+          unpack_f32x2(fma_f32x2(z23, g4.y, b4.y), y2, y3);
+          yw[2 * q] = pb_pack_bf16x2(y0, y1);
+          yw[2 * q + 1] = pb_pack_bf16x2(y2, y3);
+        }
+        *reinterpret_cast<uint4*>(gbase + off) = make_uint4(yw[0], yw[1], yw[2], yw[3]);
+      }
+    }
+    fence_proxy_async_smem();     // the tile was written through the generic proxy; the tensor core reads it
+    __syncthreads();
+    if (t == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {   // 16 channels per step: 32 bytes inside a half, halves 16 KB / 4 KB apart
+        const uint32_t a_off = (uint32_t)(((k >> 2) * kPbmHalfBytes + (k & 3) * 32) >> 4);
+        const uint32_t b_off = (uint32_t)(((k >> 2) * (kPbmWRows * 128) + (k & 3) * 32) >> 4);
+        mma_ss_f16(tmem, (uint32_t)adesc + a_off, (uint32_t)(adesc >> 32), (uint32_t)bdesc + b_off,
+                   (uint32_t)(bdesc >> 32), idesc, k > 0 ? 1u : 0u);
+      }
+      tc_commit(bar);
+    }
+    // while the MMAs run: shared -> global, coalesced, the normalised rows (256 bytes each)
+    {
+      uint4* dst = reinterpret_cast<uint4*>(p.normed + vec0 * kPbChannels);
+#pragma unroll 4
+      for (int k = t; k < rows * 16; k += kPbmRows)
+        dst[k] = *reinterpret_cast<const uint4*>(gbase + pbm_swz(k >> 4, k & 15));
+    }
+    ok = mbar_wait_bounded(bar, phase, wait_limit, &abort_flag);
+    phase ^= 1;
+    if (!__all_sync(0xffffffffu, ok)) {
+      abort_flag = 1;
+      if (atomicCAS(&g_pair_bias_status[0], 0, 1) == 0) {
+        g_pair_bias_status[1] = blockIdx.x;
+        g_pair_bias_status[2] = (int)tile;
+      }
+      ok = false;
+    }
+    if (ok) {
+      tc_fence_after();
+      uint32_t acc[32];
+      tmem_ld_x32(tmem + ((uint32_t)(warp * 32) << 16), acc);
+      tc_wait_ld();
+      tc_fence_before();
+#pragma unroll
+      for (int h = 0; h < kPbMaxHeads; ++h)
+        if (h < p.H) s_bias[h * kPbmRows + t] = __float2bfloat16_rn(__uint_as_float(acc[h]) + __uint_as_float(acc[16 + h]));
+    }
+    __syncthreads();    // s_bias complete; every thread is past its reads of the tile and of TMEM
+    if (abort_flag != 0) break;
+    for (int k = t; k < p.H * (kPbmRows / 8); k += kPbmRows) {
+      const int h = k / (kPbmRows / 8), seg = k % (kPbmRows / 8);
+      const int j = j0 + seg * 8;
+      __nv_bfloat16* bd = p.bias + ((long long)h * p.R + i) * p.bias_pitch + j;
+      if (j + 8 <= p.N) {
+        *reinterpret_cast<uint4*>(bd) = *reinterpret_cast<const uint4*>(&s_bias[h * kPbmRows + seg * 8]);
+      } else {
+        for (int e = 0; e < 8 && j + e < p.N; ++e) bd[e] = s_bias[h * kPbmRows + seg * 8 + e];
+      }
+    }
+    __syncthreads();   // the tile buffer and s_bias are reused by the next tile
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag != 0) {
+    for (int k = 0; k < 100; ++k) __nanosleep(10000);   // let MMAs still in flight finish before TMEM goes away
+    __syncthreads();
+  }
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kPbmTmemCols);
+  }
+}
+
 // ---------------------------------------------------------------- sigmoid gate
 // out = weighted * sigmoid(gate), elementwise over bf16 tensors of n elements (n a multiple of 8,
 // pointers 16-byte aligned).  Stands in for the SigmoidFwdTPP + MulTPP pair behind the core in the

@@ -185,10 +185,18 @@ void af3k_debug_set_dump(float* dump_dev);
  *   bias    [H, R, bias_pitch] bf16, bias_pitch >= N and a multiple of 8: element (h, i, j) is the
  *           logit bias of head h between positions i and j, bias[h][i][j] =
  *           sum_c bf16(normed[i][j][c]) * proj[h][c]; pad columns are not written
- * 1 <= H <= 16.  All pointers 16-byte aligned.  stream is a cudaStream_t. */
+ * 1 <= H <= 16.  All pointers 16-byte aligned.  stream is a cudaStream_t.
+ * A bf16 pair with more than four heads runs the projection on the tensor core (each fp32 weight as
+ * a bf16 high part plus a bf16 low part, fp32 accumulation); its waits are bounded and report
+ * through af3k_pair_bias_status. */
 int af3k_pair_bias(const void* pair, int32_t pair_dtype, int64_t R, int64_t N, int64_t C, int64_t H,
                    const float* gamma, const float* beta, const float* proj, float eps, void* normed,
                    void* bias, int64_t bias_pitch, void* stream);
+
+/* Status of the pair-bias producer on the current device: out4 = {1 when a bounded wait of the
+ * kernel ran out (its MMAs did not complete within the wait limit), block, tile, 0}; reading a
+ * non-zero status clears it.  Synchronises the device.  No counterpart in the reference. */
+int af3k_pair_bias_status(int32_t* out4);
 
 /* The four input projections of the grid / triangle attention block in one pass over the
  * layer-normed pair representation (c_pair = 128):  [q | k | v | gate] = x * W4^T.

@@ -28,7 +28,8 @@ def _case(R, N, H, dtype, seed, dev):
 
 
 @pytest.mark.parametrize("R,N,H,dtype", [(5, 37, 4, torch.float32), (3, 128, 4, torch.bfloat16),
-                                         (2, 300, 16, torch.bfloat16), (1, 1, 1, torch.float32),
+                                         (2, 300, 16, torch.bfloat16), (3, 200, 8, torch.bfloat16),
+                                         (1, 129, 5, torch.bfloat16), (1, 1, 1, torch.float32),
                                          (7, 264, 8, torch.float32)])
 def test_pair_bias_matches_oracle(cuda_device, R, N, H, dtype):
     pair, ln_w, ln_b, w, normed, bias = _case(R, N, H, dtype, 11 + N, cuda_device)
@@ -43,6 +44,9 @@ def test_pair_bias_matches_oracle(cuda_device, R, N, H, dtype):
     # and against the all-fp32 oracle
     assert (bias.float() - b_ref).abs().max().item() <= 2e-2 * max(1.0, scale)
     assert _capi.load().af3k_last_launch_count() == 1
+    import ctypes
+    st = (ctypes.c_int32 * 4)()
+    assert _capi.load().af3k_pair_bias_status(st) == 0 and list(st) == [0, 0, 0, 0]   # no wait of the tensor-core kernel ran out
 
 
 def test_pair_bias_full_size_properties(cuda_device):
