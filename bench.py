@@ -408,7 +408,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2",
-                    choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "grid_block", "pair_bias"])
+                    choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5", "grid_block", "pair_bias", "self_block"])
     ap.add_argument("--rows", type=int, default=0, help="override pair rows per GPU (debugging)")
     ap.add_argument("--sharded-rows", type=int, default=0, help="override the row count of the row-sharded part")
     ap.add_argument("--calls-per-step", type=int, default=CALLS_PER_STEP)
@@ -442,9 +442,9 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     name = args.workload
-    if name in ("grid_block", "pair_bias"):
+    if name in ("grid_block", "pair_bias", "self_block"):
         if rank == 0:
-            (grid_block_line if name == "grid_block" else pair_bias_line)(args, dev)
+            {"grid_block": grid_block_line, "pair_bias": pair_bias_line, "self_block": self_block_line}[name](args, dev)
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
@@ -671,6 +671,50 @@ def grid_block_line(args, dev):
                       "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
                       "ms_per_step": ms, "attention_flops": attn_flops, "projection_flops": gemm_flops,
                       "config": {"workload": f"GridSelfAttentionCpp forward, pair [{N},{N},{C}] bf16, {H} heads"},
+                      "dtype": "bf16", "data": "synthetic"}), flush=True)
+
+
+def self_block_line(args, dev):
+    """Extra workload (not the headline line): the single attention block with pair bias
+    (self_attention_cpp) at the pairformer size, N = 1536 tokens, c = 384, 16 heads of 24, bias
+    [16, N, N] bf16 - four projections (cuBLAS), the attention kernel, the sigmoid gate.  The block
+    is a handful of short launches, so it is timed both launch by launch and replayed from a CUDA
+    graph."""
+    import af3_kernels_b200 as A
+    N, C, H = (args.rows or 1536), 384, 16
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(N, C, generator=g, device=dev).to(torch.bfloat16)
+    ws = [(torch.randn(C, C, generator=g, device=dev) * C ** -0.5).to(torch.bfloat16) for _ in range(4)]
+    qb = (torch.randn(C, generator=g, device=dev) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(H, N, N, generator=g, device=dev).to(torch.bfloat16)
+    mask = torch.arange(N, device=dev) < N - 128
+    call = lambda: A.self_attention_cpp(x, mask, bias, ws[0], qb, ws[1], ws[2], ws[3], H)
+    steps, warm = args.steps, max(args.warmup, 3)
+    with torch.no_grad():
+        for _ in range(warm):
+            ref = call()
+        torch.cuda.synchronize()
+        eager = statistics.median(event_ms(call, steps))
+        graph_ms, same = None, None
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            call()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=side):
+                out = call()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        for _ in range(warm):
+            gr.replay()
+        torch.cuda.synchronize()
+        graph_ms = statistics.median(event_ms(gr.replay, steps))
+        same = bool(torch.equal(out, ref))
+    flops = 4.0 * H * N * N * (C // H) + 2.0 * N * C * 4 * C
+    print(json.dumps({"metric": "self_block_ms", "value": graph_ms, "unit": "ms", "n_gpus": 1, "steps": steps,
+                      "warmup": warm, "higher_is_better": False, "ms_launch_by_launch": eager,
+                      "ms_cuda_graph": graph_ms, "graph_equals_eager": same, "tflops_cuda_graph": flops / graph_ms / 1e9,
+                      "config": {"workload": f"self_attention_cpp, x [{N},{C}] bf16, {H} heads, bias [{H},{N},{N}] bf16"},
                       "dtype": "bf16", "data": "synthetic"}), flush=True)
 
 
