@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "af3k_set_wait_limit_cycles",
     "af3k_describe_plan",
     "af3k_pair_bias_status",
+    "af3k_pair_front",
     "af3k_debug_set_dump",
     "af3k_selftest_wait_timeout",
     "af3k_pair_bias",
@@ -118,6 +119,9 @@ def load() -> ctypes.CDLL:
     lib.af3k_pair_bias_status.argtypes = [ctypes.POINTER(ctypes.c_int32)]
     lib.af3k_qkvg_projection.restype = ctypes.c_int
     lib.af3k_qkvg_projection.argtypes = [vp, vp, i64, i64, i64, ctypes.c_float, vp, vp, vp, vp, vp, vp]
+    lib.af3k_pair_front.restype = ctypes.c_int
+    lib.af3k_pair_front.argtypes = [vp, vp, vp, ctypes.c_float, vp, i64, vp, i64, i64, i64, ctypes.c_float, vp, i64,
+                                    vp, vp, vp, vp, vp, vp]
     lib.af3k_sigmoid_gate.restype = ctypes.c_int
     lib.af3k_sigmoid_gate.argtypes = [vp, vp, vp, i64, vp]
     _lib = lib

@@ -104,7 +104,8 @@ int device_info(DeviceInfo** out) {
       return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize, pair_bias)", e);
     if ((e = cudaFuncSetAttribute(pair_bias_mma_kernel, attr, kPbmSmemBytes)) != cudaSuccess)
       return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize, pair_bias_mma)", e);
-    if ((e = cudaFuncSetAttribute(qkvg_projection_kernel, attr, (int)kProjSmemBytes)) != cudaSuccess)
+    if ((e = cudaFuncSetAttribute(qkvg_projection_kernel<false>, attr, (int)kProjSmemBytes)) != cudaSuccess ||
+        (e = cudaFuncSetAttribute(qkvg_projection_kernel<true>, attr, (int)kProjSmemBytes)) != cudaSuccess)
       return cuda_fail("cudaFuncSetAttribute(MaxDynamicSharedMemorySize, qkvg_projection)", e);
     d.attr_set = true;
   }
@@ -644,14 +645,26 @@ int af3k_pair_bias_status(int32_t* out4) {
   return AF3K_OK;
 }
 
-int af3k_qkvg_projection(const void* x, const void* w4, int64_t R, int64_t N, int64_t H, float q_scale,
-                         void* q, void* k, void* v, void* gate, int* status_dev, void* stream_v) {
+}  // extern "C"
+
+namespace {
+// Shared by af3k_qkvg_projection (x already layer-normed) and af3k_pair_front (x is the raw pair:
+// the kernel's LayerNorm warpgroup normalises every tile in shared memory and writes the bias).
+int launch_projection(const void* x, const void* w4, int64_t R, int64_t N, int64_t H, float q_scale, void* q,
+                      void* k, void* v, void* gate, int* status_dev, void* stream_v, bool with_ln,
+                      const float* gamma, const float* beta, const float* bias_w, int64_t Hb, float eps,
+                      void* bias, int64_t bias_pitch) {
   t_last_launches = 0;
   if (R < 0 || N < 0 || H < 1 || kProjC % H != 0 || (kProjC / H) % 8 != 0) return AF3K_ERR_BAD_SHAPE;
   if (R > 0x7fffffff || N > 0x7fffffff || R * N > 0x7fffff00LL * 128) return AF3K_ERR_BAD_SHAPE;
+  if (with_ln && (Hb < 1 || Hb > 4)) return AF3K_ERR_BAD_SHAPE;
+  if (with_ln && (bias_pitch < N || (bias_pitch & 7) != 0)) return AF3K_ERR_BAD_STRIDE;
   if (R == 0 || N == 0) return AF3K_OK;
   if (!x || !w4 || !q || !k || !v || !gate) return AF3K_ERR_NULL_POINTER;
+  if (with_ln && (!gamma || !beta || !bias_w || !bias)) return AF3K_ERR_NULL_POINTER;
   if (!aligned16(x) || !aligned16(w4) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(gate))
+    return AF3K_ERR_BAD_ALIGNMENT;
+  if (with_ln && (!aligned16(gamma) || !aligned16(beta) || !aligned16(bias_w) || !aligned16(bias)))
     return AF3K_ERR_BAD_ALIGNMENT;
   DeviceInfo* dev = nullptr;
   int rc = device_info(&dev);
@@ -678,18 +691,39 @@ int af3k_qkvg_projection(const void* x, const void* w4, int64_t R, int64_t N, in
     if (r != CUDA_SUCCESS) return driver_fail("cuTensorMapEncodeTiled(w4)", (int)r);
   }
   ProjParams p;
+  std::memset(&p, 0, sizeof(p));
   p.M = M; p.N = (int)N; p.H = (int)H; p.D = kProjC / (int)H; p.q_scale = q_scale;
   p.q = static_cast<__nv_bfloat16*>(q); p.k = static_cast<__nv_bfloat16*>(k);
   p.v = static_cast<__nv_bfloat16*>(v); p.g = static_cast<__nv_bfloat16*>(gate);
   p.status = status_dev;
   p.wait_limit = wait_limit_cycles();
+  p.gamma = gamma; p.beta = beta; p.bias_w = bias_w; p.bias = static_cast<__nv_bfloat16*>(bias);
+  p.bias_pitch = bias_pitch; p.Hb = (int)Hb; p.R = (int)R; p.eps = eps;
   const long long n_tiles = (M + 127) / 128;
   const unsigned grid = (unsigned)(n_tiles < dev->sm_count ? n_tiles : dev->sm_count);
-  qkvg_projection_kernel<<<grid, kProjThreads, kProjSmemBytes, reinterpret_cast<cudaStream_t>(stream_v)>>>(p, tm_x, tm_w);
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_v);
+  if (with_ln) qkvg_projection_kernel<true><<<grid, kProjLnThreads, kProjSmemBytes, stream>>>(p, tm_x, tm_w);
+  else         qkvg_projection_kernel<false><<<grid, kProjThreads, kProjSmemBytes, stream>>>(p, tm_x, tm_w);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail("launch qkvg_projection_kernel", e);
   t_last_launches = 1;
   return AF3K_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int af3k_qkvg_projection(const void* x, const void* w4, int64_t R, int64_t N, int64_t H, float q_scale,
+                         void* q, void* k, void* v, void* gate, int* status_dev, void* stream_v) {
+  return launch_projection(x, w4, R, N, H, q_scale, q, k, v, gate, status_dev, stream_v, false, nullptr, nullptr,
+                           nullptr, 0, 0.f, nullptr, 0);
+}
+
+int af3k_pair_front(const void* pair, const float* gamma, const float* beta, float eps, const float* bias_w,
+                    int64_t Hb, const void* w4, int64_t R, int64_t N, int64_t H, float q_scale, void* bias,
+                    int64_t bias_pitch, void* q, void* k, void* v, void* gate, int* status_dev, void* stream_v) {
+  return launch_projection(pair, w4, R, N, H, q_scale, q, k, v, gate, status_dev, stream_v, true, gamma, beta,
+                           bias_w, Hb, eps, bias, bias_pitch);
 }
 
 int af3k_sigmoid_gate(const void* weighted, const void* gate, void* out, int64_t n, void* stream_v) {

@@ -21,6 +21,20 @@
 // and stores with consecutive lanes on consecutive 16-byte pieces (full 64 / 128-byte runs).
 // The two column halves have their own full / empty barriers, so the MMAs of one half run while
 // the other half is being drained.
+//
+// Second instantiation (kLn): x is the RAW pair representation and a fourth warpgroup stands
+// between the TMA and the MMAs,
+//   warps 12-19 two LayerNorm warpgroups, one per stage of the x ring (a tile's two walks are a
+//               chain of about a thousand dependent instructions per thread, twice the tile's share
+//               of the HBM time, so two tiles are normalised at a time): thread t owns row t -
+//               moments, normalise in place, round to bf16 - and, from the rounded values, the
+//               per-head logit bias of the row (up to four heads), stored straight into [H, R, N];
+// which takes the normalised pair's round trip through HBM (one write and one read of M x 256
+// bytes) out of the block.  Measured at N = 768: 0.232 ms against 0.073 + 0.140 ms for the stand-alone
+// producer followed by the first instantiation - the row walks are latency-bound and only two tiles
+// per SM are in them at a time (the stand-alone producer has five CTAs per SM) -, so the modules do
+// not use this instantiation by default.  Reference: src/af3_kernels/Attention.py:51-52 and :152-153 in front of
+// the projections above.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -34,6 +48,12 @@ namespace af3k {
 constexpr int kProjC = 128;                 // input channels (c_pair)
 constexpr int kProjOut = 4 * kProjC;        // q | k | v | gate
 constexpr int kProjThreads = 384;
+constexpr int kProjLnThreads = 640;         // + the two LayerNorm warpgroups
+// Registers of the kLn variant: launched with 96 per thread (61440, the pool setmaxnreg works in),
+// then 128 x 72 (producer, MMA issuer) + 256 x 128 (epilogue) + 256 x 72 (LayerNorm) = 60416.
+constexpr int kProjLnRegsMisc = 72, kProjLnRegsEpi = 128, kProjLnRegsNorm = 72;
+static_assert(128 * kProjLnRegsMisc + 256 * kProjLnRegsEpi + 256 * kProjLnRegsNorm <= 96 * kProjLnThreads,
+              "setmaxnreg totals exceed the launch allocation");
 constexpr int kProjStages = 2;              // x tiles in flight
 constexpr uint32_t kProjXTileBytes = 128 * kProjC * 2;          // 32 KB: two 128B-swizzled panels of 64 channels
 constexpr uint32_t kProjWBytes = kProjOut * kProjC * 2;         // 128 KB: two panels of 64 channels x 512 rows
@@ -52,6 +72,14 @@ struct ProjParams {
   __nv_bfloat16* g;      // [M, 128]
   int* status;           // same status word as the attention kernel
   long long wait_limit;
+  // kLn only: LayerNorm weight / bias [128], bias projection [Hb, 128] (all fp32), output [Hb, R, bias_pitch]
+  const float* gamma;
+  const float* beta;
+  const float* bias_w;
+  __nv_bfloat16* bias;
+  long long bias_pitch;
+  int Hb, R;
+  float eps;
 };
 
 struct ProjBar {
@@ -60,7 +88,8 @@ struct ProjBar {
   static constexpr int x_empty = 1 + kProjStages;        // [kProjStages]
   static constexpr int acc_full = 1 + 2 * kProjStages;   // [2] column halves
   static constexpr int acc_empty = 3 + 2 * kProjStages;  // [2]
-  static constexpr int count = 5 + 2 * kProjStages;
+  static constexpr int x_ready = 5 + 2 * kProjStages;    // [kProjStages]  tile normalised in place (kLn)
+  static constexpr int count = 5 + 3 * kProjStages;
 };
 
 __device__ __forceinline__ void proj_timeout(const ProjParams& p, volatile int* abort_flag, int bar) {
@@ -91,7 +120,8 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint
       : "memory");
 }
 
-__global__ void __launch_bounds__(kProjThreads, 1)
+template <bool kLn>
+__global__ void __launch_bounds__(kLn ? kProjLnThreads : kProjThreads, 1)
 qkvg_projection_kernel(const __grid_constant__ ProjParams p, const __grid_constant__ CUtensorMap tm_x,
                        const __grid_constant__ CUtensorMap tm_w) {
   extern __shared__ uint8_t proj_smem_raw[];
@@ -114,6 +144,7 @@ qkvg_projection_kernel(const __grid_constant__ ProjParams p, const __grid_consta
     for (int i = 0; i < kProjStages; ++i) {
       mbar_init(bars + 8u * (ProjBar::x_full + i), 1);
       mbar_init(bars + 8u * (ProjBar::x_empty + i), 1);
+      mbar_init(bars + 8u * (ProjBar::x_ready + i), 4);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bars + 8u * (ProjBar::acc_full + i), 1);
@@ -130,6 +161,11 @@ qkvg_projection_kernel(const __grid_constant__ ProjParams p, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = tmem_base_slot;
 
+  if (kLn) {
+    if (warp < 4) setmaxnreg_dec<kProjLnRegsMisc>();
+    else if (warp < 12) setmaxnreg_inc<kProjLnRegsEpi>();
+    else setmaxnreg_dec<kProjLnRegsNorm>();
+  }
   if (warp == 0) {
     // ---- producer (whole warp runs the control flow, one lane issues)
     const bool leader = elect_one();
@@ -164,7 +200,7 @@ qkvg_projection_kernel(const __grid_constant__ ProjParams p, const __grid_consta
     uint32_t n = 0;
     for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++n) {
       const uint32_t st = n % kProjStages;
-      AF3K_PROJ_WAIT(ProjBar::x_full + st, (n / kProjStages) & 1);
+      AF3K_PROJ_WAIT((kLn ? ProjBar::x_ready : ProjBar::x_full) + st, (n / kProjStages) & 1);
       for (int nh = 0; nh < 2; ++nh) {
         // the epilogue warps of this half must have read the previous tile's columns
         if (n >= 1) AF3K_PROJ_WAIT(ProjBar::acc_empty + nh, (n - 1) & 1);
@@ -183,7 +219,7 @@ qkvg_projection_kernel(const __grid_constant__ ProjParams p, const __grid_consta
         __syncwarp();
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 4 && warp < 12) {
     // ---- epilogue: warp quarter (TMEM lanes) x column half
     const int quarter = warp & 3, half = (warp - 4) >> 2;
     const uint32_t t_base = tmem + ((uint32_t)(quarter * 32) << 16) + half * 256;
@@ -258,6 +294,108 @@ qkvg_projection_kernel(const __grid_constant__ ProjParams p, const __grid_consta
           if ((row_ok >> it) & 1u) *reinterpret_cast<uint4*>(dst + (which == 3 ? off_g[it] : off_qkv[it])) = o;
         }
         __syncwarp();      // the patch is rewritten by the next 64 columns
+      }
+    }
+  }
+  else if (kLn && warp >= 12) {
+    // ---- LayerNorm in place + bias projection: warpgroup wg takes the tiles of ring stage wg,
+    // thread t owns row t of the tile
+    static_assert(kProjStages == 2, "one LayerNorm warpgroup per ring stage");
+    const int wg = (warp - 12) >> 2;
+    const int t = ((warp - 12) & 3) * 32 + lane;
+    uint32_t n = (uint32_t)wg;
+    for (long long tile = blockIdx.x + (long long)wg * gridDim.x; tile < n_tiles; tile += 2LL * gridDim.x, n += 2) {
+      const uint32_t st = n % kProjStages;
+      AF3K_PROJ_WAIT(ProjBar::x_full + st, (n / kProjStages) & 1);
+      const uint32_t tile_s = x_smem + st * kProjXTileBytes;
+      // 16-byte piece c8 of the row: panel c8 / 8, position (c8 % 8) ^ (row % 8) inside the 128-byte row
+      auto piece = [&](int c8) { return tile_s + (uint32_t)((c8 >> 3) * (kProjXTileBytes / 2) + t * 128 + (((c8 & 7) ^ (t & 7)) << 4)); };
+      auto load8 = [&](int c8, float (&x)[8]) {
+        uint32_t w[4];
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(piece(c8)));
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { x[2 * e] = __uint_as_float(w[e] << 16); x[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u); }
+      };
+      // mean and (biased) variance in one walk, as moments about the row's first element
+      float pivot;
+      {
+        float x[8];
+        load8(0, x);
+        pivot = x[0];
+      }
+      const uint64_t npivot2 = pack_f32x2(-pivot, -pivot);
+      uint64_t s1a = pack_f32x2(0.f, 0.f), s1b = s1a, s2a = s1a, s2b = s1a;
+#pragma unroll 4
+      for (int c8 = 0; c8 < 16; ++c8) {
+        float x[8];
+        load8(c8, x);
+#pragma unroll
+        for (int e = 0; e < 8; e += 4) {
+          const uint64_t da = add_f32x2(pack_f32x2(x[e], x[e + 1]), npivot2);
+          const uint64_t db = add_f32x2(pack_f32x2(x[e + 2], x[e + 3]), npivot2);
+          s1a = add_f32x2(s1a, da); s1b = add_f32x2(s1b, db);
+          s2a = fma_f32x2(da, da, s2a); s2b = fma_f32x2(db, db, s2b);
+        }
+      }
+      float s1lo, s1hi, s2lo, s2hi;
+      unpack_f32x2(add_f32x2(s1a, s1b), s1lo, s1hi);
+      unpack_f32x2(add_f32x2(s2a, s2b), s2lo, s2hi);
+      const float m1 = (s1lo + s1hi) * (1.0f / kProjC);
+      const float mean = pivot + m1;
+      const float var = fmaxf((s2lo + s2hi) * (1.0f / kProjC) - m1 * m1, 0.f);
+      const float rstd = rsqrtf(var + p.eps);
+      const uint64_t rstd2 = pack_f32x2(rstd, rstd);
+      const float nmr = -mean * rstd;
+      const uint64_t nmr2 = pack_f32x2(nmr, nmr);
+      uint64_t acc2[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) acc2[h] = pack_f32x2(0.f, 0.f);
+#pragma unroll 4
+      for (int c8 = 0; c8 < 16; ++c8) {
+        float x[8];
+        load8(c8, x);
+        uint32_t yw[4];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          // the constants are the same for every thread: warp-wide broadcasts out of L1
+          const ulonglong2 g4 = __ldg(reinterpret_cast<const ulonglong2*>(p.gamma + c8 * 8 + 4 * q));
+          const ulonglong2 b4 = __ldg(reinterpret_cast<const ulonglong2*>(p.beta + c8 * 8 + 4 * q));
+          const uint64_t z01 = fma_f32x2(pack_f32x2(x[4 * q], x[4 * q + 1]), rstd2, nmr2);
+          const uint64_t z23 = fma_f32x2(pack_f32x2(x[4 * q + 2], x[4 * q + 3]), rstd2, nmr2);
+          float y0, y1, y2, y3;
+          unpack_f32x2(fma_f32x2(z01, g4.x, b4.x), y0, y1);
+          unpack_f32x2(fma_f32x2(z23, g4.y, b4.y), y2, y3);
+          yw[2 * q] = pack_bf16x2(y0, y1);
+          yw[2 * q + 1] = pack_bf16x2(y2, y3);
+          // the bias projection sees the rounded values
+          const uint64_t r01 = pack_f32x2(__uint_as_float(yw[2 * q] << 16), __uint_as_float(yw[2 * q] & 0xffff0000u));
+          const uint64_t r23 = pack_f32x2(__uint_as_float(yw[2 * q + 1] << 16), __uint_as_float(yw[2 * q + 1] & 0xffff0000u));
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            if (h < p.Hb) {
+              const ulonglong2 w4 = __ldg(reinterpret_cast<const ulonglong2*>(p.bias_w + h * kProjC + c8 * 8 + 4 * q));
+              acc2[h] = fma_f32x2(r23, w4.y, fma_f32x2(r01, w4.x, acc2[h]));
+            }
+          }
+        }
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(piece(c8)), "r"(yw[0]), "r"(yw[1]), "r"(yw[2]), "r"(yw[3]) : "memory");
+      }
+      fence_proxy_async_smem();     // the tile was rewritten through the generic proxy; the tensor core reads it
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8u * (ProjBar::x_ready + st));
+      // the row's bias values: consecutive threads are consecutive j of one pair row i (or the next one)
+      const long long m = tile * 128 + t;
+      if (m < p.M) {
+        const long long i = m / p.N;
+        const int j = (int)(m - i * p.N);
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          if (h < p.Hb) {
+            float lo, hi;
+            unpack_f32x2(acc2[h], lo, hi);
+            p.bias[((long long)h * p.R + i) * p.bias_pitch + j] = __float2bfloat16_rn(lo + hi);
+          }
+        }
       }
     }
   }

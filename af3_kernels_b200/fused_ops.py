@@ -89,6 +89,51 @@ def _fused_projection_ok(x: torch.Tensor, head: int) -> bool:
             and x.is_contiguous() and x.data_ptr() % 16 == 0 and x.numel() > 0)
 
 
+def pair_front(pair: torch.Tensor, ln_weight: torch.Tensor, ln_bias: torch.Tensor, eps: float,
+               bias_weight: torch.Tensor, w4: torch.Tensor, head: int, q_scale: float):
+    """The whole front of the grid block in one pass over the RAW pair [R, N, 128] bf16
+    (``af3k_pair_front``): LayerNorm, the pair-bias projection + permute, and the q / k / v / gate
+    projections.  Returns (bias [Hb, R, N] bf16 view with 16-byte aligned rows, q, k, v
+    [R, head, N, 128 / head], gate [R, N, 128]); the normalised pair itself never reaches HBM."""
+    R, N, C = pair.shape
+    D = C // head
+    dev = pair.device
+    Hb = bias_weight.shape[0]
+    gamma = ln_weight.detach().to(device=dev, dtype=torch.float32).contiguous()
+    beta = ln_bias.detach().to(device=dev, dtype=torch.float32).contiguous()
+    bw = bias_weight.detach().to(device=dev, dtype=torch.float32).contiguous()
+    pitch = (N + 7) // 8 * 8
+    bias = torch.empty((Hb, R, pitch), dtype=torch.bfloat16, device=dev)
+    q = torch.empty((R, head, N, D), dtype=torch.bfloat16, device=dev)
+    k = torch.empty_like(q)
+    v = torch.empty_like(q)
+    g = torch.empty((R, N, C), dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        _capi.check(_capi.load().af3k_pair_front(
+            pair.data_ptr(), gamma.data_ptr(), beta.data_ptr(), ctypes.c_float(eps), bw.data_ptr(), Hb,
+            w4.data_ptr(), R, N, head, ctypes.c_float(q_scale), bias.data_ptr(), pitch, q.data_ptr(), k.data_ptr(),
+            v.data_ptr(), g.data_ptr(), _status_buffer(dev).data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return bias[:, :, :N], q, k, v, g
+
+
+def pair_front_ok(pair: torch.Tensor, head: int, bias_heads: int) -> bool:
+    return pair.is_cuda and pair.dim() == 3 and _fused_projection_ok(pair, head) and 1 <= bias_heads <= 4
+
+
+def grid_block_from_raw_pair(pair, mask, ln_weight, ln_bias, eps, bias_weight, q_proj, k_proj, v_proj,
+                             gating_query, out_proj, head: int) -> torch.Tensor:
+    """LayerNorm + pair bias + ``attention_block`` for a raw bf16 pair [R, N, 128]: the fused front,
+    the attention core, the sigmoid gate and the output projection."""
+    R, N, C = pair.shape
+    D = C // head
+    w4 = _stacked_projection_weights(q_proj, k_proj, v_proj, gating_query)
+    bias, q, k, v, gate = pair_front(pair, ln_weight, ln_bias, eps, bias_weight, w4, head, D ** -0.5)
+    weighted = torch.empty((R, N, head, D), dtype=torch.bfloat16, device=pair.device)
+    dot_product_attention(q, k, v, mask, bias, softmax_scale=1.0, out=weighted.permute(0, 2, 1, 3))
+    gated = sigmoid_gate(weighted.view(R, N, C), gate)
+    return torch.matmul(gated, _as_bf16(out_proj))
+
+
 def attention_block(
     pair: torch.Tensor,
     mask: torch.Tensor,

@@ -216,6 +216,22 @@ int af3k_pair_bias_status(int32_t* out4);
 int af3k_qkvg_projection(const void* x, const void* w4, int64_t R, int64_t N, int64_t H, float q_scale,
                          void* q, void* k, void* v, void* gate, int* status_dev, void* stream);
 
+/* The whole front of the grid / triangle attention block in one pass over the RAW pair
+ * representation (bf16, c_pair = 128):
+ *     x = LayerNorm(pair);  bias = (x W_b^T).permute(2, 0, 1);  [q | k | v | gate] = x W4^T
+ * i.e. af3k_pair_bias followed by af3k_qkvg_projection without the normalised pair's round trip
+ * through HBM (src/af3_kernels/Attention.py:51-52, :152-153 and
+ * src/csrc/dot_product_attention.cpp:285-338).  x is rounded to bf16 before both projections, as
+ * the stand-alone entry points do.
+ *
+ *   pair   [R, N, 128] bf16, contiguous;  gamma, beta [128] fp32;  bias_w [Hb, 128] fp32, 1 <= Hb <= 4
+ *   bias   [Hb, R, bias_pitch] bf16, bias_pitch >= N and a multiple of 8 (pad columns not written)
+ *   w4, q, k, v, gate, H, q_scale, status_dev: as in af3k_qkvg_projection
+ * All pointers 16-byte aligned.  stream is a cudaStream_t. */
+int af3k_pair_front(const void* pair, const float* gamma, const float* beta, float eps, const float* bias_w,
+                    int64_t Hb, const void* w4, int64_t R, int64_t N, int64_t H, float q_scale, void* bias,
+                    int64_t bias_pitch, void* q, void* k, void* v, void* gate, int* status_dev, void* stream);
+
 /* out = weighted * sigmoid(gate), elementwise over n bf16 elements (n a multiple of 8; all three
  * pointers 16-byte aligned; out may be weighted).  Stands in for the SigmoidFwdTPP + MulTPP pair
  * behind the attention core in the reference's fused blocks

@@ -171,3 +171,34 @@ def test_self_block_replays_from_a_cuda_graph(cuda_device):
         torch.cuda.synchronize(dev)
     assert torch.equal(out, ref)
     assert read_status(dev)[0] == 0
+
+
+def test_fused_front_matches_the_two_kernels_it_replaces(cuda_device):
+    """af3k_pair_front (LayerNorm + pair bias + q/k/v/gate projections from the raw pair) against
+    af3k_pair_bias followed by af3k_qkvg_projection: both round the normalised pair to bf16 before
+    the projections; odd sizes cover tiles that straddle pair rows and the ragged last tile."""
+    from af3_kernels_b200.fused_ops import _stacked_projection_weights, pair_front, qkvg_projection
+    from af3_kernels_b200.pair_bias import layernorm_pair_bias
+    dev = cuda_device
+    for R, N, H, Hb in ((5, 200, 4, 4), (3, 128, 4, 2), (2, 37, 8, 1), (130, 130, 4, 4)):
+        g = torch.Generator().manual_seed(100 + N)
+        pair = (torch.randn(R, N, 128, generator=g) * 2.0 + 0.3).to(torch.bfloat16).to(dev)
+        ln_w = (1.0 + 0.2 * torch.randn(128, generator=g)).to(dev)
+        ln_b = (0.1 * torch.randn(128, generator=g)).to(dev)
+        bw = (torch.randn(Hb, 128, generator=g) * 0.3).to(dev)
+        ws = [(torch.randn(128, 128, generator=g) * 128 ** -0.5).to(torch.bfloat16).to(dev) for _ in range(4)]
+        w4 = _stacked_projection_weights(*ws)
+        D = 128 // H
+        normed, bias_ref = layernorm_pair_bias(pair, ln_w, ln_b, bw)
+        q_ref, k_ref, v_ref, g_ref = qkvg_projection(normed, w4, H, D ** -0.5)
+        bias, q, k, v, gate = pair_front(pair, ln_w, ln_b, 1e-5, bw, w4, H, D ** -0.5)
+        torch.cuda.synchronize(dev)
+        assert read_status(dev)[0] == 0
+        # the two LayerNorms order their arithmetic differently, so a normalised value may land on the
+        # neighbouring bf16 now and then: the projections agree to a few bf16 ulps of their scale
+        for a, b in ((q, q_ref), (k, k_ref), (v, v_ref), (gate, g_ref)):
+            s_ = b.float().abs().max().item()
+            assert (a.float() - b.float()).abs().max().item() <= 2.0 ** -6 * s_
+            assert (a.float() - b.float()).abs().mean().item() <= 2.0 ** -10 * s_
+        scale = bias_ref.float().abs().max().item()
+        assert (bias.float() - bias_ref.float()).abs().max().item() <= 2.0 ** -7 * scale + 1e-3
