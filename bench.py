@@ -770,7 +770,7 @@ def pair_bias_line(args, dev):
 
 # DRAM bytes per launch of attention_kernel from one ncu capture (dram__bytes_read.sum +
 # dram__bytes_write.sum), scaled to the full launch by pair rows; see profiles/.
-TRAFFIC_BYTES = {"cfg2": 552.8e6}   # 4 x (118.18 + 20.01) MB captured on 192 of 768 pair rows
+TRAFFIC_BYTES = {"cfg2": 545.2e6}   # 4 x (118.23 + 18.08) MB captured on 192 of 768 pair rows
 
 if __name__ == "__main__":
     main()
