@@ -662,6 +662,7 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
                                              int nv, uint32_t bias_row, uint32_t row7, float scale,
                                              bool first_kt, bool wait_prev_pv, int prev_pv_bar,
                                              uint32_t prev_pv_parity, float& m_run, float& l_run,
+                                             int next_s_bar, uint32_t next_s_parity, bool& next_ready,
                                              long long* ts = nullptr) {
   uint32_t xr[kTile];
   float mt;
@@ -781,6 +782,10 @@ __device__ __forceinline__ bool softmax_tile(const Ctx& c, float* dbg, int wg, i
     }
   }
   if (ts != nullptr) ts[6] = clock64();     // last exponential issued
+  // The next tile's logits are normally finished by now: ask while the P stores drain, so that the
+  // barrier's round trip (about two hundred cycles even when the phase is complete) is not paid
+  // between two tiles.
+  next_ready = __all_sync(0xffffffffu, mbar_test_wait(bar_addr(c, next_s_bar), next_s_parity));
   tc_wait_st();
   if (ts != nullptr) ts[4] = clock64();   // P stored
   float s0, s1, s2, s3;
@@ -801,6 +806,7 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
   // running statistics of the warpgroup's (at most two) streams, kept in registers
   float m_st[2] = {-INFINITY, -INFINITY}, l_st[2] = {0.f, 0.f};
   uint32_t ucnt = 0, bcount = 0, icount = 0;         // tiles done by this warpgroup, bias tiles, items
+  bool s_ready = false;                              // the next tile's s_full phase was seen complete already
   // position of tiles in the CTA-wide order (all streams): gives the K/V stage a tile used
   uint32_t kt_stage = 0, kt_round = 0;                // ring stage / lap of stream 0's tile at the current key tile
   uint32_t prev_stage = 0, prev_round = 0;            // the same for this warpgroup's last tile
@@ -833,7 +839,7 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
           ts = reinterpret_cast<long long*>(p.debug + kDbgFloats) + ((size_t)wg * kDbgTimelineTiles + ucnt) * 8;
         if (ts != nullptr) ts[0] = clock64();
         if (kDebug) last_ts = ts;
-        AF3K_WAIT_WARP(c, BarIdx::s_full + wg, ucnt & 1);
+        if (!s_ready) AF3K_WAIT_WARP(c, BarIdx::s_full + wg, ucnt & 1);
         tc_fence_after();
         if (ts != nullptr) ts[1] = clock64();
         const uint32_t o_taddr = c.tmem + lane_sel + kOCol + s * p.nv;
@@ -842,7 +848,7 @@ __device__ void softmax_role(const Ctx& c, int wg, int wq, int lane) {
           dbg = p.debug + (size_t)row * kTile;
         if (!softmax_tile<kTcBias>(c, dbg, wg, lane, s_taddr, p_taddr, o_taddr, p.nv, bias_row, row & 7, scale,
                                    kt == 0, ucnt > 0, BarIdx::kv_empty + (int)prev_stage, prev_round & 1, m_run,
-                                   l_run, ts))
+                                   l_run, BarIdx::s_full + wg, (ucnt + 1) & 1, s_ready, ts))
           return;
         ++ucnt;
         {
