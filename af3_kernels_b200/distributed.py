@@ -50,9 +50,14 @@ class RowShardedAttention:
         # N = 2 048, fp8 q/k): 7.17 ms with every SM and four pieces, 6.97 ms with eight SMs left free
         # and eight pieces; capping NCCL's own CTAs (NCCL_MAX_CTAS) only made the transfers slower.
         self.comm_sms = comm_sms
-        # how the pieces travel on CUDA ranks: "sendrecv" (grouped point-to-point, in place), "broadcast"
-        # (one per rank, in place) or "allgather" (one collective into a staging buffer + a copy)
-        self.exchange = "sendrecv"
+        # How the pieces travel on CUDA ranks: "copy" (peer-to-peer copies into the peers' result buffers,
+        # which live in symmetric memory: copy engines move the data, no SM is taken from the attention
+        # kernel), "sendrecv" (grouped NCCL point-to-point, in place), "broadcast" (one per rank, in
+        # place), "allgather" (one collective into a staging buffer + a copy); "auto" = "copy" where
+        # symmetric memory can be set up, else "sendrecv".
+        self.exchange = "auto"
+        self._symm = {}
+        self._copy_streams = None
         # the CUDA operator writes into a caller-provided ``out``; a stand-in (CPU tests) returns its result
         self.writes_in_place = attention_fn is None
         if attention_fn is None:
@@ -83,6 +88,31 @@ class RowShardedAttention:
         b, e, _ = row_partition(rows, self.world_size, self.rank)
         return full[b:e]
 
+    def _symmetric_result(self, shape, dtype, device):
+        """One of two result buffers in symmetric memory (alternating per call, so that a result stays
+        valid until the call after the next starts) with the peers' views of it, or None when
+        symmetric memory is not available."""
+        key = (tuple(shape), dtype, device.index)
+        ent = self._symm.get(key)
+        if ent is None:
+            try:
+                import torch.distributed._symmetric_memory as symm_mem
+                group = self.group if self.group is not None else dist.group.WORLD
+                bufs = []
+                for _ in range(2):
+                    t = symm_mem.empty(shape, dtype=dtype, device=device)
+                    hdl = symm_mem.rendezvous(t, group)
+                    peers = [t if r == self.rank else hdl.get_buffer(r, shape, dtype) for r in range(self.world_size)]
+                    bufs.append((t, hdl, peers))
+                ent = {"bufs": bufs, "turn": 0}
+            except Exception:           # no symmetric memory on this system / build
+                ent = {"bufs": None, "turn": 0}
+            self._symm[key] = ent
+        if ent["bufs"] is None:
+            return None
+        ent["turn"] ^= 1
+        return ent["bufs"][ent["turn"]]
+
     # ------------------------------------------------------------------ compute
     def forward_local(self, q, k, v, mask, bias) -> torch.Tensor:
         """Attention over this rank's rows only; the output stays row-sharded."""
@@ -96,7 +126,9 @@ class RowShardedAttention:
         the full problem, so every rank computes each piece of its block straight into its own
         slot and the pieces of the other ranks arrive in place: per piece one broadcast per rank
         (each rank is the root of its own slot), issued on a side stream while the next piece is
-        computed.  Nothing is copied after the collective."""
+        computed.  Nothing is copied after the collective.  With ``exchange`` "copy" (the default where
+        symmetric memory works) the result is a view of one of two buffers that alternate per call: it
+        stays valid until the call after the next one."""
         ws, rank = self.world_size, self.rank
         b, e, split = row_partition(rows, ws, rank)
         local_rows = e - b
@@ -105,7 +137,22 @@ class RowShardedAttention:
         _, H, N, D = q.shape
         piece = (split + self.comm_split - 1) // self.comm_split
         out_dtype = torch.bfloat16 if q.is_cuda else q.dtype
-        full = torch.empty((ws, split, H, N, D), dtype=out_dtype, device=q.device)
+        exchange = self.exchange
+        symm = None
+        if q.is_cuda and ws > 1 and exchange in ("auto", "copy"):
+            symm = self._symmetric_result((ws, split, H, N, D), out_dtype, q.device)
+            if symm is None and exchange == "copy":
+                raise RuntimeError("exchange='copy' needs symmetric memory, which could not be set up")
+        if exchange == "auto":
+            exchange = "copy" if symm is not None else "sendrecv"
+        if exchange == "copy":
+            full, hdl, peer_full = symm
+            # nobody may still be writing into (or, two calls back, reading from) this buffer
+            hdl.barrier(channel=0)
+            if self._copy_streams is None:
+                self._copy_streams = [torch.cuda.Stream(device=q.device) for _ in range(4)]
+        else:
+            full = torch.empty((ws, split, H, N, D), dtype=out_dtype, device=q.device)
         if local_rows < split:
             full[rank, local_rows:].zero_()        # the padded tail of a ragged split, dropped at the end
         roots = [dist.get_global_rank(self.group, r) if self.group is not None else r for r in range(ws)]
@@ -125,18 +172,29 @@ class RowShardedAttention:
                 slot = full[rank, lo:hi]
                 if self.writes_in_place:
                     kw = {}
-                    if q.is_cuda and ws > 1 and self.comm_sms > 0:
+                    if q.is_cuda and ws > 1 and self.comm_sms > 0 and exchange != "copy":
                         sms = torch.cuda.get_device_properties(q.device).multi_processor_count
                         kw["max_ctas"] = max(1, sms - self.comm_sms)
                     self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias, out=slot, **kw)
                 else:
                     slot.copy_(self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias))
-            if use_streams:
+            if use_streams and exchange == "copy":
+                # this rank's piece into every peer's buffer, spread over a few streams so that several
+                # copy engines work at once
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream(q.device))
+                for r in range(ws):
+                    if r != rank and p1 > p0:
+                        cs = self._copy_streams[r % len(self._copy_streams)]
+                        cs.wait_event(ev)
+                        with torch.cuda.stream(cs):
+                            peer_full[r][rank, p0:p1].copy_(full[rank, p0:p1], non_blocking=True)
+            elif use_streams:
                 ev = torch.cuda.Event()
                 ev.record(torch.cuda.current_stream(q.device))
                 with torch.cuda.stream(self._comm_stream):
                     self._comm_stream.wait_event(ev)
-                    if self.exchange == "sendrecv":
+                    if exchange == "sendrecv":
                         # one grouped launch per piece: this rank's slot goes to every peer while
                         # theirs arrive, both directions of every link busy at once
                         ops = []
@@ -147,7 +205,7 @@ class RowShardedAttention:
                         if ops:
                             for w in dist.batch_isend_irecv(ops):
                                 w.wait()       # orders the comm stream behind the transfer; the host does not block
-                    elif self.exchange == "allgather":
+                    elif exchange == "allgather":
                         # one collective per piece into a staging buffer, then one strided copy into place
                         tmp = torch.empty((ws, p1 - p0, H, N, D), dtype=out_dtype, device=q.device)
                         dist.all_gather_into_tensor(tmp, full[rank, p0:p1].contiguous(), group=self.group)
@@ -162,7 +220,14 @@ class RowShardedAttention:
         for w in works:
             if not w.wait(timeout=_timedelta(timeout_s)):
                 raise RuntimeError("broadcast of an output piece did not complete")
-        if use_streams:
+        if use_streams and exchange == "copy":
+            # every rank's copies are behind it when it reaches the barrier, so past the barrier every
+            # rank's buffer is complete
+            cur = torch.cuda.current_stream(q.device)
+            for cs in self._copy_streams:
+                cur.wait_stream(cs)
+            hdl.barrier(channel=1)
+        elif use_streams:
             torch.cuda.current_stream(q.device).wait_stream(self._comm_stream)
             full.record_stream(self._comm_stream)
         record_comm_time("AG Attn", time.time() - t0, full.numel() * full.element_size())
