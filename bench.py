@@ -392,12 +392,13 @@ def row_sharded_report(args, O, dev, world, rank):
         "gather_inbound_bytes_per_gpu": inbound, "gather_floor_ms": floor_ms,
         "gather_floor_basis": f"{NVLINK_GBS_PER_DIRECTION:.0f} GB/s per direction per GPU (nominal NVLink 5)",
         "gather_floor_ms_at_770_gbs": inbound / 770e9 * 1e3,
-        "comm_split": sharder.comm_split, "comm_sms": comm_sms, "exchange": sharder.exchange,
+        "comm_split": sharder.comm_split, "comm_sms": comm_sms, "exchange": sharder.last_exchange,
         "total_ms_kernel_on_all_sms": total_ms_all_sms, "E2_kernel_on_all_sms": t1_ms / (world * total_ms_all_sms),
         "sharded_equals_single": bool(eq.item() == 1),
         "definitions": "E1 = t1 / (N * slowest rank's kernel on its row block); E2 = t1 / (N * time of "
-                       "RowShardedAttention.forward: kernel pieces that leave comm_sms SMs free + the pieces' "
-                       "in-place exchange (NCCL grouped send/recv) on a side stream)",
+                       "RowShardedAttention.forward: kernel pieces + the pieces' in-place exchange on side streams "
+                       "(exchange = copy: peer-to-peer copies into the peers' result buffers in symmetric memory; "
+                       "sendrecv: grouped NCCL send/recv beside kernels that leave comm_sms SMs free))",
     }
 
 
