@@ -47,11 +47,18 @@ def _worker(rank, ws, port, rows, ret):
         b_in = bias.clone() if rank == 0 else torch.zeros_like(bias)
         m_in = (mask.clone() if rank == 0 else torch.zeros_like(mask)).view(torch.uint8)
         op.broadcast_shared(b_in, m_in)
-        full = op.forward(op.shard(q, rows), op.shard(k, rows), op.shard(v, rows),
-                          op.shard(m_in.view(torch.bool), rows), b_in, rows)
-        torch.cuda.synchronize()
-        ok = full.shape == single.shape and torch.equal(full, single) and read_status(dev)[0] == 0
-        ret[rank] = bool(ok)
+        ok, used = True, []
+        # every form of the exchange, the default first ("auto": peer copies into symmetric memory
+        # where that can be set up); two calls each, since the result buffers alternate
+        for exchange in ("auto", "sendrecv", "broadcast", "allgather"):
+            op.exchange = exchange
+            for _ in range(2):
+                full = op.forward(op.shard(q, rows), op.shard(k, rows), op.shard(v, rows),
+                                  op.shard(m_in.view(torch.bool), rows), b_in, rows)
+                torch.cuda.synchronize()
+                ok = ok and full.shape == single.shape and torch.equal(full, single) and read_status(dev)[0] == 0
+            used.append(op.last_exchange)
+        ret[rank] = bool(ok) and used[1:] == ["sendrecv", "broadcast", "allgather"]
     finally:
         dist.barrier()
         dist.destroy_process_group()
