@@ -4,7 +4,6 @@ loads unchanged.  The forward passes run on CUDA through ``attention_block``.
 """
 from __future__ import annotations
 
-import time
 from math import ceil
 
 import torch
@@ -13,7 +12,7 @@ import torch.nn as nn
 
 from . import pair_bias
 from .fused_ops import attention_block, grid_block_from_raw_pair, pair_front_ok
-from .tools import pad_to_size, profile, record_comm_time
+from .tools import profile
 
 
 class GridSelfAttentionCpp(nn.Module):
@@ -77,51 +76,39 @@ class DistributedGridSelfAttentionCpp(GridSelfAttentionCpp):
     computes the rows ``[rank * ceil(N / ws), (rank + 1) * ceil(N / ws))``; the bias is computed
     redundantly on every rank from the replicated pair, the mask is sliced by row, and the row
     blocks are exchanged in ``COMM_SPLIT`` pieces.  The reference overlaps gather *i* with the
-    compute of piece *i + 1* from a helper thread; here the exchange (one in-place broadcast per rank
-    and piece) runs on a side CUDA stream."""
+    compute of piece *i + 1* from a helper thread; here the exchange runs on side CUDA streams
+    (``RowShardedAttention.gather_rows``: peer copies into symmetric memory, or NCCL)."""
 
     def __init__(self, c_pair: int = 128, num_head: int = 4, transpose: bool = False):
         super().__init__(c_pair, num_head, transpose)
-        self._comm_stream = None
+        self._sharder = None
 
     @profile("B200 Distributed GridSelfAttention")
     def forward(self, pair: torch.Tensor, mask: torch.Tensor, COMM_SPLIT: int = 4) -> torch.Tensor:
+        from .distributed import RowShardedAttention
         rk, ws = dist.get_rank(), dist.get_world_size()
         dtype = pair.dtype
         seq_len = pair.shape[0]
         split_size = ceil(seq_len / ws)
         rows = slice(split_size * rk, split_size * (rk + 1))
-        local_mask = pad_to_size(mask[rows], split_size, 0)
+        local_mask = mask[rows]
 
         pair, bias = self._norm_and_bias(pair)
         bias = bias.contiguous()
         if self.transpose:
             pair = pair.permute(1, 0, 2)
-        chunk = pad_to_size(pair[rows], split_size, 0)
-        gathered = torch.empty((ws, split_size, *pair.shape[1:]), device=pair.device, dtype=pair.dtype)
+        chunk = pair[rows]
+        if self._sharder is None:
+            self._sharder = RowShardedAttention()
+        self._sharder.comm_split = COMM_SPLIT
+        weights = self._weights()
 
-        piece = ceil(split_size / COMM_SPLIT)
-        if self._comm_stream is None:
-            self._comm_stream = torch.cuda.Stream(device=pair.device)
-        start = time.time()
-        for begin in range(0, split_size, piece):
-            end = min(split_size, begin + piece)
+        def compute(lo, hi, slot, kw):
             # this rank's piece goes straight into its slot of the result; the other ranks' pieces
-            # arrive in place, one broadcast per rank, on the side stream
-            gathered[rk, begin:end].copy_(attention_block(chunk[begin:end], local_mask[begin:end], bias,
-                                                          *self._weights(), self.num_head))
-            ready = torch.cuda.Event()
-            ready.record(torch.cuda.current_stream(pair.device))
-            with torch.cuda.stream(self._comm_stream):
-                self._comm_stream.wait_event(ready)
-                for r in range(ws):
-                    dist.broadcast(gathered[r, begin:end], src=r)
-        torch.cuda.current_stream(pair.device).wait_stream(self._comm_stream)
-        gathered.record_stream(self._comm_stream)
-        record_comm_time("AG Attn", time.time() - start,
-                         gathered.numel() * gathered.element_size() * (ws - 1) / ws)
+            # arrive in place while the next piece is computed (RowShardedAttention.gather_rows)
+            slot.copy_(attention_block(chunk[lo:hi], local_mask[lo:hi], bias, *weights, self.num_head))
 
-        out = gathered.view(ws * split_size, *pair.shape[1:])[:seq_len]
+        out = self._sharder.gather_rows(seq_len, tuple(pair.shape[1:]), pair.dtype, pair.device, compute)
         if self.transpose:
             out = out.permute(1, 0, 2)
         return out.contiguous().to(dtype)

@@ -123,27 +123,48 @@ class RowShardedAttention:
 
     def forward(self, q, k, v, mask, bias, rows: int, timeout_s: float = 60.0) -> torch.Tensor:
         """q, k, v, mask: this rank's row block (``shard`` of the full tensors).  Returns the
-        full ``[rows, H, N, D]`` output on every rank.
-
-        The result buffer is laid out ``[rank, row in block, H, N, D]``, which is the row order of
-        the full problem, so every rank computes each piece of its block straight into its own
-        slot and the pieces of the other ranks arrive in place: per piece one broadcast per rank
-        (each rank is the root of its own slot), issued on a side stream while the next piece is
-        computed.  Nothing is copied after the collective.  With ``exchange`` "copy" (the default where
-        symmetric memory works) the result is a view of one of two buffers that alternate per call: it
-        stays valid until the call after the next one."""
+        full ``[rows, H, N, D]`` output on every rank (see ``gather_rows`` for how the pieces travel
+        and how long the result stays valid)."""
         ws, rank = self.world_size, self.rank
         b, e, split = row_partition(rows, ws, rank)
         local_rows = e - b
         if q.shape[0] != local_rows:
             raise ValueError(f"rank {rank} expected {local_rows} local rows, got {q.shape[0]}")
         _, H, N, D = q.shape
-        piece = (split + self.comm_split - 1) // self.comm_split
         out_dtype = torch.bfloat16 if q.is_cuda else q.dtype
+
+        def compute(lo, hi, slot, kw):
+            m = None
+            if mask is not None:
+                m = mask[lo:hi] if mask.dim() >= 2 and mask.shape[0] == local_rows else mask
+            if self.writes_in_place:
+                self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias, out=slot, **kw)
+            else:
+                slot.copy_(self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias))
+
+        return self.gather_rows(rows, (H, N, D), out_dtype, q.device, compute, timeout_s)
+
+    def gather_rows(self, rows: int, tail, dtype, device, compute, timeout_s: float = 60.0) -> torch.Tensor:
+        """Runs ``compute(lo, hi, slot, kw)`` for the pieces ``[lo, hi)`` of this rank's row block -
+        it must fill ``slot`` (``[hi - lo, *tail]``), passing ``kw`` on to the attention operator - and
+        returns the full ``[rows, *tail]`` result on every rank.
+
+        The result buffer is laid out ``[rank, row in block, *tail]``, which is the row order of the
+        full problem, so every rank computes each piece of its block straight into its own slot and
+        the pieces of the other ranks arrive in place while the next piece is computed.  Nothing is
+        copied after the exchange.  With ``exchange`` "copy" (the default where symmetric memory
+        works) the result is a view of one of two buffers that alternate per call: it stays valid
+        until the call after the next one."""
+        ws, rank = self.world_size, self.rank
+        b, e, split = row_partition(rows, ws, rank)
+        local_rows = e - b
+        tail = tuple(tail)
+        on_gpu = device.type == "cuda"
+        piece = (split + self.comm_split - 1) // self.comm_split
         exchange = self.exchange
         symm = None
-        if q.is_cuda and ws > 1 and exchange in ("auto", "copy"):
-            symm = self._symmetric_result((ws, split, H, N, D), out_dtype, q.device)
+        if on_gpu and ws > 1 and exchange in ("auto", "copy"):
+            symm = self._symmetric_result((ws, split) + tail, dtype, device)
             if symm is None and exchange == "copy":
                 raise RuntimeError("exchange='copy' needs symmetric memory, which could not be set up")
         if exchange == "auto":
@@ -155,39 +176,32 @@ class RowShardedAttention:
             hdl.barrier(channel=0)
             n_cs = self.copy_streams if self.copy_streams > 0 else max(1, ws - 1)
             if self._copy_streams is None or len(self._copy_streams) != n_cs:
-                self._copy_streams = [torch.cuda.Stream(device=q.device) for _ in range(n_cs)]
+                self._copy_streams = [torch.cuda.Stream(device=device) for _ in range(n_cs)]
         else:
-            full = torch.empty((ws, split, H, N, D), dtype=out_dtype, device=q.device)
+            full = torch.empty((ws, split) + tail, dtype=dtype, device=device)
         if local_rows < split:
             full[rank, local_rows:].zero_()        # the padded tail of a ragged split, dropped at the end
         roots = [dist.get_global_rank(self.group, r) if self.group is not None else r for r in range(ws)]
 
-        use_streams = q.is_cuda
+        use_streams = on_gpu
         if use_streams and self._comm_stream is None:
-            self._comm_stream = torch.cuda.Stream(device=q.device)
+            self._comm_stream = torch.cuda.Stream(device=device)
+        kw = {}
+        if on_gpu and ws > 1 and self.comm_sms > 0 and exchange != "copy":
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
+            kw["max_ctas"] = max(1, sms - self.comm_sms)
         works = []
         t0 = time.time()
         for p0 in range(0, split, piece):
             p1 = min(split, p0 + piece)
             lo, hi = min(p0, local_rows), min(p1, local_rows)
             if hi > lo:
-                m = None
-                if mask is not None:
-                    m = mask[lo:hi] if mask.dim() >= 2 and mask.shape[0] == local_rows else mask
-                slot = full[rank, lo:hi]
-                if self.writes_in_place:
-                    kw = {}
-                    if q.is_cuda and ws > 1 and self.comm_sms > 0 and exchange != "copy":
-                        sms = torch.cuda.get_device_properties(q.device).multi_processor_count
-                        kw["max_ctas"] = max(1, sms - self.comm_sms)
-                    self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias, out=slot, **kw)
-                else:
-                    slot.copy_(self.attention_fn(q[lo:hi], k[lo:hi], v[lo:hi], m, bias))
+                compute(lo, hi, full[rank, lo:hi], kw)
             if use_streams and exchange == "copy":
-                # this rank's piece into every peer's buffer, spread over a few streams so that several
+                # this rank's piece into every peer's buffer, one stream per peer so that several
                 # copy engines work at once
                 ev = torch.cuda.Event()
-                ev.record(torch.cuda.current_stream(q.device))
+                ev.record(torch.cuda.current_stream(device))
                 for r in range(ws):
                     if r != rank and p1 > p0:
                         cs = self._copy_streams[r % len(self._copy_streams)]
@@ -196,7 +210,7 @@ class RowShardedAttention:
                             peer_full[r][rank, p0:p1].copy_(full[rank, p0:p1], non_blocking=True)
             elif use_streams:
                 ev = torch.cuda.Event()
-                ev.record(torch.cuda.current_stream(q.device))
+                ev.record(torch.cuda.current_stream(device))
                 with torch.cuda.stream(self._comm_stream):
                     self._comm_stream.wait_event(ev)
                     if exchange == "sendrecv":
@@ -212,7 +226,7 @@ class RowShardedAttention:
                                 w.wait()       # orders the comm stream behind the transfer; the host does not block
                     elif exchange == "allgather":
                         # one collective per piece into a staging buffer, then one strided copy into place
-                        tmp = torch.empty((ws, p1 - p0, H, N, D), dtype=out_dtype, device=q.device)
+                        tmp = torch.empty((ws, p1 - p0) + tail, dtype=dtype, device=device)
                         dist.all_gather_into_tensor(tmp, full[rank, p0:p1].contiguous(), group=self.group)
                         full[:, p0:p1].copy_(tmp)
                         tmp.record_stream(self._comm_stream)
@@ -228,15 +242,15 @@ class RowShardedAttention:
         if use_streams and exchange == "copy":
             # every rank's copies are behind it when it reaches the barrier, so past the barrier every
             # rank's buffer is complete
-            cur = torch.cuda.current_stream(q.device)
+            cur = torch.cuda.current_stream(device)
             for cs in self._copy_streams:
                 cur.wait_stream(cs)
             hdl.barrier(channel=1)
         elif use_streams:
-            torch.cuda.current_stream(q.device).wait_stream(self._comm_stream)
+            torch.cuda.current_stream(device).wait_stream(self._comm_stream)
             full.record_stream(self._comm_stream)
         record_comm_time("AG Attn", time.time() - t0, full.numel() * full.element_size())
-        return full.view(ws * split, H, N, D)[:rows]
+        return full.view((ws * split,) + tail)[:rows]
 
 
 def _timedelta(seconds: float):

@@ -83,3 +83,61 @@ def test_sharded_output_equals_single_gpu(cuda_device, rows):
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     assert all(ret.get(r) for r in range(ws)), dict(ret)
 
+
+
+def _module_worker(rank, ws, port, n, ret):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import datetime
+    import torch.distributed as dist
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    try:
+        import af3_kernels_b200 as A
+        torch.manual_seed(11)                                    # same weights on every rank
+        plain = A.GridSelfAttentionCpp(128, 4).to(dev).to(torch.bfloat16).eval()
+        shard = A.DistributedGridSelfAttentionCpp(128, 4).to(dev).to(torch.bfloat16).eval()
+        shard.load_state_dict(plain.state_dict())
+        g = torch.Generator(device=dev).manual_seed(12)
+        pair = torch.randn(n, n, 128, generator=g, device=dev).to(torch.bfloat16)
+        mask = torch.rand(n, n, generator=g, device=dev) >= 0.1
+        with torch.no_grad():
+            ref = plain(pair, mask)
+            ok = True
+            for _ in range(2):                                   # the result buffers alternate per call
+                out = shard(pair, mask, COMM_SPLIT=3)
+                torch.cuda.synchronize()
+                # row blocks of other sizes may take another GEMM kernel in the output projection:
+                # equal to a bf16 ulp of the largest value, not bit for bit
+                tol = 2.0 ** -7 * ref.float().abs().max().item()
+                ok = ok and out.shape == ref.shape and (out.float() - ref.float()).abs().max().item() <= tol
+        ret[rank] = bool(ok)
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n", [160, 135])
+def test_distributed_grid_module_equals_plain_module(cuda_device, n):
+    """DistributedGridSelfAttentionCpp on two or more GPUs against GridSelfAttentionCpp on one, for a
+    row count the ranks share evenly and one they do not."""
+    ws = min(torch.cuda.device_count(), 4)
+    if ws < 2:
+        pytest.skip("needs at least two CUDA devices")
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_module_worker, args=(r, ws, port, n, ret)) for r in range(ws)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert all(ret.get(r) for r in range(ws)), dict(ret)
