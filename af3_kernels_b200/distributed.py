@@ -199,12 +199,16 @@ class RowShardedAttention:
                 compute(lo, hi, full[rank, lo:hi], kw)
             if use_streams and exchange == "copy":
                 # this rank's piece into every peer's buffer, one stream per peer so that several
-                # copy engines work at once
+                # copy engines work at once.  Every rank starts with its right-hand neighbour: with
+                # all ranks going through the peers in the same order, everybody's first copy lands
+                # on the same GPU (measured on 8 GPUs, copies alone: 204 GB/s out of every GPU
+                # against 700 GB/s in this order).
                 ev = torch.cuda.Event()
                 ev.record(torch.cuda.current_stream(device))
-                for r in range(ws):
-                    if r != rank and p1 > p0:
-                        cs = self._copy_streams[r % len(self._copy_streams)]
+                for kk in range(1, ws):
+                    if p1 > p0:
+                        r = (rank + kk) % ws
+                        cs = self._copy_streams[(kk - 1) % len(self._copy_streams)]
                         cs.wait_event(ev)
                         with torch.cuda.stream(cs):
                             peer_full[r][rank, p0:p1].copy_(full[rank, p0:p1], non_blocking=True)
