@@ -61,6 +61,7 @@ class RowShardedAttention:
         self._symm = {}
         self._copy_streams = None
         self.last_exchange = None       # what the last forward used
+        self.symm_error = None          # why symmetric memory could not be set up, if it could not
         # the CUDA operator writes into a caller-provided ``out``; a stand-in (CPU tests) returns its result
         self.writes_in_place = attention_fn is None
         if attention_fn is None:
@@ -108,8 +109,12 @@ class RowShardedAttention:
                     peers = [t if r == self.rank else hdl.get_buffer(r, shape, dtype) for r in range(self.world_size)]
                     bufs.append((t, hdl, peers))
                 ent = {"bufs": bufs, "turn": 0}
-            except Exception:           # no symmetric memory on this system / build
+            except Exception as exc:    # no symmetric memory on this system / build: NCCL carries the pieces
+                self.symm_error = f"{type(exc).__name__}: {exc}"
                 ent = {"bufs": None, "turn": 0}
+            # two result shapes are kept (each costs two full-size buffers); an older one is dropped
+            while len(self._symm) >= 2:
+                self._symm.pop(next(iter(self._symm)))
             self._symm[key] = ent
         if ent["bufs"] is None:
             return None
