@@ -56,6 +56,19 @@ def _worker(rank, ws, port, rows, comm_split, ret):
                                  op.shard(mask_b, rows), bias)
         b, e = (rows + ws - 1) // ws * rank, min(rows, (rows + ws - 1) // ws * (rank + 1))
         ok = ok and torch.equal(local, single[b:e])
+        # the gather on its own, with another row payload and a caller-supplied piece function
+        # (what the distributed grid module does with its whole block per piece)
+        table = torch.arange(rows * 15, dtype=torch.float32).reshape(rows, 5, 3)
+        mine = table[b:e]
+        seen = []
+
+        def compute(lo, hi, slot, kw):
+            seen.append((lo, hi))
+            slot.copy_(mine[lo:hi] * 2.0)
+
+        got = op.gather_rows(rows, (5, 3), torch.float32, torch.device("cpu"), compute)
+        ok = ok and torch.equal(got, table * 2.0)
+        ok = ok and sum(hi - lo for lo, hi in seen) == max(e - b, 0) and all(hi > lo for lo, hi in seen)
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
